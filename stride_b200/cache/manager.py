@@ -51,7 +51,8 @@ def _runtime():
         for name, extra in (("acquire_slot", []), ("release_slot", [ctypes.c_int]), ("pages_needed", [ctypes.c_int, ctypes.c_int, _I32P]),
                             ("free_slots", [_I32P, ctypes.c_int]), ("free_list", [ctypes.c_int, _I32P, ctypes.c_int]),
                             ("ensure", [ctypes.c_int, ctypes.c_int]), ("trim", [ctypes.c_int, ctypes.c_int]),
-                            ("take_dirty", [_I32P, ctypes.c_int]), ("held_count", [ctypes.c_int, ctypes.c_int]), ("check", [])):
+                            ("take_dirty", [_I32P, ctypes.c_int]), ("held_count", [ctypes.c_int, ctypes.c_int]), ("check", []),
+                            ("set_keep", [ctypes.c_int, ctypes.c_int])):
             fn = getattr(lib, "sb_pool_" + name)
             fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_void_p, *extra]
         lib.sb_pool_free_pages.restype, lib.sb_pool_free_pages.argtypes = None, [ctypes.c_void_p, _I32P]
@@ -79,19 +80,21 @@ class CacheGroup:
     page_size: int
     num_pages: int
     entries: list = field(default_factory=list)      # schedule entries served, in order
-    arena: Optional[torch.Tensor] = None             # [pages, len(entries), 2, kv_heads, page_size, head_dim]
+    arena: Optional[torch.Tensor] = None             # [pages, len(entries), planes, kv_heads, page_size, head_dim]
     table_host: Optional[np.ndarray] = None          # [slots, max_pages] int32, NO_PAGE where nothing is held
     table_pinned: Optional[torch.Tensor] = None      # the tensor behind table_host (pinned when the arena is on a GPU)
     table_device: Optional[torch.Tensor] = None
     manager: Optional["CacheManager"] = None
     index: int = 0
+    planes: int = 2                                  # 2: keys and values; 1: one row per token that serves as both
+    keep_first: int = 0                              # with a window: the first tokens of a request that stay seen (their pages are never trimmed)
 
     @property
     def page_bytes(self) -> int:
-        return len(self.entries) * 2 * self.kv_heads * self.page_size * self.head_dim * torch.finfo(self.dtype).bits // 8
+        return len(self.entries) * self.planes * self.kv_heads * self.page_size * self.head_dim * torch.finfo(self.dtype).bits // 8
 
     def layer_view(self, entry: int) -> torch.Tensor:
-        """[pages, 2, kv_heads, page_size, head_dim] of one schedule entry."""
+        """[pages, planes, kv_heads, page_size, head_dim] of one schedule entry."""
         return self.arena[:, self.entries.index(entry)]
 
     @property
@@ -110,7 +113,7 @@ class CacheGroup:
 @dataclass
 class LayerCache:
     """What a mixer gets for one schedule entry."""
-    pages: Optional[torch.Tensor] = None        # [pages, 2, kv_heads, page_size, head_dim]
+    pages: Optional[torch.Tensor] = None        # [pages, planes, kv_heads, page_size, head_dim]
     block_table: Optional[torch.Tensor] = None  # [slots, max_pages] int32 on the device
     page_size: int = 0
     state: Optional[torch.Tensor] = None        # [slots, *state_shape]
@@ -166,15 +169,21 @@ class CacheManager:
             if need.kind != "pages":
                 raise CacheError(f"unknown cache need kind '{need.kind}'")
             dtype = need.dtype
-            sig = (need.kv_heads, need.head_dim, need.window, dtype)
+            planes = int(getattr(need, "planes", 2))
+            if planes not in (1, 2):
+                raise CacheError(f"a page has one or two planes, not {planes}")
+            keep = int(getattr(need, "keep_first", 0)) if need.window > 0 else 0
+            if keep < 0:
+                raise CacheError(f"a window keeps no fewer than 0 first tokens, not {keep}")
+            sig = (need.kv_heads, need.head_dim, need.window, dtype, planes, keep)
             for gi, g in enumerate(self.groups):
-                if (g.kv_heads, g.head_dim, g.window, g.dtype) == sig:
+                if (g.kv_heads, g.head_dim, g.window, g.dtype, g.planes, g.keep_first) == sig:
                     g.entries.append(i)
                     self.entry_group[i] = gi
                     break
             else:
                 self.groups.append(CacheGroup(need.kv_heads, need.head_dim, need.window, dtype, page_size, 0, [i],
-                                              manager=self, index=len(self.groups)))
+                                              manager=self, index=len(self.groups), planes=planes, keep_first=keep))
                 self.entry_group[i] = len(self.groups) - 1
         for i, j in self.entry_shared.items():
             if j not in self.entry_group and j not in self.states:
@@ -190,7 +199,7 @@ class CacheManager:
                 raise CacheError("the cache pool is smaller than one page")
         for g in self.groups:
             g.num_pages = num_pages
-            g.arena = torch.zeros((num_pages + 1, len(g.entries), 2, g.kv_heads, page_size, g.head_dim), dtype=g.dtype, device=self.device)
+            g.arena = torch.zeros((num_pages + 1, len(g.entries), g.planes, g.kv_heads, page_size, g.head_dim), dtype=g.dtype, device=self.device)
             pin = self.device.type == "cuda"
             g.table_pinned = torch.full((max_slots + 1, self.max_pages_per_seq), NO_PAGE, dtype=torch.int32, pin_memory=pin)
             g.table_host = g.table_pinned.numpy()        # a view: the pool's edits go straight into the pinned copy
@@ -206,6 +215,9 @@ class CacheManager:
                                               self.live.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)), shuffle_seed)
         if not self._pool:
             raise CacheError(self._lib.sb_last_error().decode())
+        for g in self.groups:
+            if g.keep_first and self._lib.sb_pool_set_keep(self._pool, g.index, g.keep_first) < 0:
+                raise CacheError(self._lib.sb_last_error().decode())
         self._counts = np.zeros(max(n, 1), dtype=np.int32)
         self._counts_p = self._counts.ctypes.data_as(_I32P)
         self._dirty = np.zeros((max(n, 1) * (max_slots + 1), 2), dtype=np.int32)

@@ -7,8 +7,14 @@
 // takes up to two branches into `dst` (the residual, or another branch) in 32-bit and leaves the branch buffers zero,
 // which is the state the next sublayer expects to find them in. The order of the additions is fixed.
 //
+// The fold with a norm on the way (a sublayer whose result is RMS-normed before it joins the residual):
+//
+//   y[r, :] = ca * (a + ..)[r, :] + cb * (b + ..)[r, :];   dst[r, j] += gain[j] * y[r, j] / sqrt(mean_j(y[r, j]^2) + eps)
+//
 // A second kernel adds a row-scaled copy of the sublayer's input: dst[r, :] += (sum of `count` columns of w[r, :]) * x[r, :],
-// what experts that pass their input through contribute to a routed feed-forward.
+// what experts that pass their input through contribute to a routed feed-forward. A third adds another stream's rows and one
+// vector to every row: dst[r, :] = ((dst[r, :] + pending sums) + other[r, :]) + vector[:], what stands in front of a pass over a group
+// of layers that takes the embedding output in again and marks the pass with a stored vector.
 #include "common.cuh"
 #include "step_ops.h"
 
@@ -104,6 +110,48 @@ __global__ void __launch_bounds__(256) branch_fold_kernel(float* __restrict__ ds
   }
 }
 
+// A block per row: the row's values (the branches read and cleared as above) stay in shared memory between the sum of squares and the
+// scaled add. The squares are added by a thread in ascending columns, then over the block in `block_sum`'s order.
+template <class TG>
+__global__ void __launch_bounds__(256) branch_norm_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ gain, int W,
+                                                               float eps) {
+  extern __shared__ float row_values[];
+  __shared__ float red[32];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
+  const bool two = b.h != nullptr || b.partials != nullptr;
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = mul(source_value<float>(a, row + c), a.c);
+    if (two) v = add(v, mul(source_value<float>(b, row + c), b.c));
+    row_values[c] = v;
+    sq = fmaf(v, v, sq);
+  }
+  const float scale = 1.0f / sqrtf(sb::block_sum(sq, red) / static_cast<float>(W) + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = mul(row_values[c], scale);
+    if (gain != nullptr) v = mul(v, sb::widen(gain[c]));
+    dst[row + c] = add(dst[row + c], v);
+  }
+}
+
+template <class TV>
+__global__ void __launch_bounds__(256) stream_add_kernel(float* __restrict__ dst, const float* __restrict__ partials, int n_partials, int64_t stride,
+                                                         const float* __restrict__ other, const TV* __restrict__ vector, int W) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
+  const Source pending{nullptr, partials, partials ? n_partials : 0, stride, 1.0f};
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = dst[row + c];
+    if (partials != nullptr) v = add(v, source_value<float>(pending, row + c));
+    if (other != nullptr) v = add(v, other[row + c]);
+    if (vector != nullptr) v = add(v, sb::widen(vector[c]));
+    dst[row + c] = v;
+  }
+}
+
 template <class TX>
 __global__ void __launch_bounds__(256) row_scaled_add_kernel(float* __restrict__ dst, const TX* __restrict__ x, const float* __restrict__ w, int ldw,
                                                              int first, int count, int W) {
@@ -142,6 +190,38 @@ SB_EXPORT int sb_branch_fold(float* dst, float* a, const float* pa, int na, int6
   return sb::check_launch("sb_branch_fold");
 }
 
+SB_EXPORT int sb_branch_norm_fold(float* dst, float* a, const float* pa, int na, int64_t sa, float ca, float* b, const float* pb, int nb,
+                                  int64_t sb_, float cb, const void* gain, int gain_dtype, float eps, int n, int W, cudaStream_t stream) {
+  if (n <= 0 || W <= 0) return 0;
+  if (a == nullptr && pa == nullptr) return sb::fail("sb_branch_norm_fold: the first branch has neither a buffer nor partial sums");
+  const Source A{a, pa, pa ? na : 0, sa, ca}, B{b, pb, pb ? nb : 0, sb_, cb};
+  const size_t smem = static_cast<size_t>(W) * sizeof(float);
+  if (smem > 160 * 1024) return sb::fail("sb_branch_norm_fold: a row of %d elements does not fit the row buffer", W);
+  const int threads = W >= 1024 ? 256 : 128;
+  if (gain == nullptr || gain_dtype == 0) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_norm_fold_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(branch_norm_fold_kernel<float>, dim3(n), dim3(threads), smem, stream, dst, A, B, static_cast<const float*>(gain), W, eps);
+  } else if (gain_dtype == 1) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_norm_fold_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(branch_norm_fold_kernel<bf16>, dim3(n), dim3(threads), smem, stream, dst, A, B, static_cast<const bf16*>(gain), W, eps);
+  } else {
+    return sb::fail("sb_branch_norm_fold: unsupported gain dtype %d", gain_dtype);
+  }
+  return sb::check_launch("sb_branch_norm_fold");
+}
+
+SB_EXPORT int sb_stream_add(float* dst, const float* partials, int n_partials, int64_t stride, const float* other, const void* vector,
+                            int vector_dtype, int n, int W, cudaStream_t stream) {
+  if (n <= 0 || W <= 0) return 0;
+  if (vector == nullptr || vector_dtype == 0)
+    sb::launch_pdl(stream_add_kernel<float>, dim3(n), dim3(256), 0, stream, dst, partials, n_partials, stride, other, static_cast<const float*>(vector), W);
+  else if (vector_dtype == 1)
+    sb::launch_pdl(stream_add_kernel<bf16>, dim3(n), dim3(256), 0, stream, dst, partials, n_partials, stride, other, static_cast<const bf16*>(vector), W);
+  else
+    return sb::fail("sb_stream_add: unsupported vector dtype %d", vector_dtype);
+  return sb::check_launch("sb_stream_add");
+}
+
 SB_EXPORT int sb_row_scaled_add(float* dst, const void* x, int x_dtype, const float* w, int ldw, int first, int count, int n, int W,
                                 cudaStream_t stream) {
   if (n <= 0 || W <= 0 || count <= 0) return 0;
@@ -166,6 +246,28 @@ SB_EXPORT int sb_op_branch_fold(const SbOp* op, const SbStep* s, void* stream) {
   return sb_branch_fold(ptr<float>(op->i[0]), ptr<float>(op->i[1]), ptr<const float>(op->i[2]), partial_count(op->i[3], op->i[4], s->n), stride,
                         static_cast<float>(op->f[0]), ptr<float>(op->i[5]), ptr<const float>(op->i[6]), partial_count(op->i[7], op->i[4], s->n),
                         stride, static_cast<float>(op->f[1]), ptr<const void>(op->i[8]), (int)op->i[9], s->n, W, static_cast<cudaStream_t>(stream));
+}
+
+// i: as sb_op_branch_fold      f: 0 ca, 1 cb, 2 eps
+SB_EXPORT int sb_op_branch_norm_fold(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int W = (int)op->i[10];
+  const int64_t stride = static_cast<int64_t>(s->n) * W;
+  return sb_branch_norm_fold(ptr<float>(op->i[0]), ptr<float>(op->i[1]), ptr<const float>(op->i[2]), partial_count(op->i[3], op->i[4], s->n), stride,
+                             static_cast<float>(op->f[0]), ptr<float>(op->i[5]), ptr<const float>(op->i[6]), partial_count(op->i[7], op->i[4], s->n),
+                             stride, static_cast<float>(op->f[1]), ptr<const void>(op->i[8]), (int)op->i[9], static_cast<float>(op->f[2]), s->n, W,
+                             static_cast<cudaStream_t>(stream));
+}
+
+// i: 0 dst, 1 pending partial sums (flat, or 0), 2 their K ranges S, 3 most tokens with a buffer per range, 4 the other stream (or 0),
+//    5 the vector (or 0), 6 its dtype, 7 W
+SB_EXPORT int sb_op_stream_add(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int W = (int)op->i[7];
+  return sb_stream_add(ptr<float>(op->i[0]), ptr<const float>(op->i[1]), partial_count(op->i[2], op->i[3], s->n), static_cast<int64_t>(s->n) * W,
+                       ptr<const float>(op->i[4]), ptr<const void>(op->i[5]), (int)op->i[6], s->n, W, static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 dst, 1 x, 2 x dtype, 3 w, 4 ldw, 5 first column, 6 columns, 7 W

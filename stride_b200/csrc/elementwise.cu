@@ -23,7 +23,7 @@ using bf16 = __nv_bfloat16;
 template <class TW>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int vocab, const int32_t* __restrict__ slots,
-                             const int32_t* __restrict__ sampled, float* __restrict__ copy) {
+                             const int32_t* __restrict__ sampled, float* __restrict__ copy, float scale) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int row = blockIdx.x;
@@ -35,7 +35,7 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __res
   // `copy`: a second place for the same rows, for models whose later layers read the embedding again
   float* dst2 = copy != nullptr ? copy + static_cast<int64_t>(row) * H : nullptr;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = ok ? sb::widen(src[i]) : 0.0f;
+    const float v = ok ? __fmul_rn(sb::widen(src[i]), scale) : 0.0f;     // (a scale of 1 changes no bit)
     dst[i] = v;
     if (dst2 != nullptr) dst2[i] = v;
   }
@@ -315,12 +315,12 @@ SB_EXPORT int sb_concat_rows(float* a, const float* partials, int n_partials, in
 }
 
 SB_EXPORT int sb_embed(const int32_t* tokens, const void* table, int table_dtype, float* out, int n, int H, int vocab,
-                       const int32_t* slots, const int32_t* sampled, float* copy, cudaStream_t stream) {
+                       const int32_t* slots, const int32_t* sampled, float* copy, float scale, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (table_dtype == 0)
-    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab, slots, sampled, copy);
+    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab, slots, sampled, copy, scale);
   else if (table_dtype == 1)
-    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab, slots, sampled, copy);
+    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab, slots, sampled, copy, scale);
   else
     return sb::fail("sb_embed: unsupported table dtype %d", table_dtype);
   return sb::check_launch("sb_embed");
@@ -378,12 +378,13 @@ SB_EXPORT int sb_gather_rows(const float* in, const float* partials, int n_parti
 
 // ------------------------------------------------------------------ operations of the native step program (step_ops.h)
 // i: 0 table, 1 table dtype, 2 out (float32 [n, H]), 3 H, 4 vocab, 5 the table of last sampled tokens (or 0),
-//    6 a second buffer [n, H] that receives the same rows (or 0)
+//    6 a second buffer [n, H] that receives the same rows (or 0)      f: 0 the factor on every element
 SB_EXPORT int sb_op_embed(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   const int32_t* sampled = ptr<const int32_t>(op->i[5]);
   return sb_embed(tokens(s), ptr<const void>(op->i[0]), (int)op->i[1], ptr<float>(op->i[2]), s->n, (int)op->i[3], (int)op->i[4],
-                  sampled ? slots(s) : nullptr, sampled, ptr<float>(op->i[6]), static_cast<cudaStream_t>(stream));
+                  sampled ? slots(s) : nullptr, sampled, ptr<float>(op->i[6]), static_cast<float>(op->f[0]),
+                  static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 qkv partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 cos_sin, 5 rotary_dim,

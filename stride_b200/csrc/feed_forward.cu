@@ -63,7 +63,9 @@ __global__ void __launch_bounds__(1024) polynorm_kernel(const float* __restrict_
 }
 
 // One warp per token. logits [n][ldz] float32, correction [X] (float32 or bfloat16), weights out [n][X].
-template <class TC>
+// BIASED: the correction is a bias of the router (z + correction are the logits), the experts with the largest logits are chosen and
+// weigh by the softmax over the chosen logits alone: exp(z - max) / (sum of the chosen exp(z - max)), the largest logit being one of them.
+template <class TC, bool BIASED>
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, const TC* __restrict__ correction, float* __restrict__ weights, int n,
                                  int X, int top, float scale) {
   sb::grid_launch_dependents();
@@ -76,13 +78,14 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int x = lane + 32 * i;
-    v[i] = x < X ? z[x] : -INFINITY;
+    v[i] = x < X ? (BIASED ? __fadd_rn(z[x], sb::widen(correction[x])) : z[x]) : -INFINITY;
     m = fmaxf(m, v[i]);
   }
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  float sum = 0.0f;
+  float sum = 0.0f, logit[kPer];
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
+    logit[i] = v[i];
     v[i] = lane + 32 * i < X ? expf(v[i] - m) : 0.0f;
     sum += v[i];
   }
@@ -91,8 +94,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int x = lane + 32 * i;
-    score[i] = v[i] / sum;
-    choice[i] = x < X ? score[i] + sb::widen(correction[x]) : -INFINITY;
+    score[i] = BIASED ? v[i] : v[i] / sum;
+    choice[i] = x < X ? (BIASED ? logit[i] : score[i] + sb::widen(correction[x])) : -INFINITY;
     out[i] = 0.0f;
   }
   float picked_sum = 0.0f;
@@ -125,7 +128,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
     s = __shfl_sync(0xffffffffu, s, at & 31);
     picked_sum += s;
   }
-  const float norm = picked_sum + 1e-20f;
+  const float norm = BIASED ? picked_sum : picked_sum + 1e-20f;
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int x = lane + 32 * i;
@@ -133,8 +136,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
   }
 }
 
-// A block per row; the row's expert weights in shared memory first.
-template <class TO>
+// A block per row; the row's expert weights in shared memory first. GATED: an expert has 2 F rows of `up`, F gate rows and then F up
+// rows, and its hidden activation is silu(gate) * up instead of relu(up)^2.
+template <class TO, bool GATED>
 __global__ void __launch_bounds__(256) moe_activate_kernel(const float* __restrict__ up, int n_partials, int64_t partial_stride,
                                                            const float* __restrict__ weights, int ldw, TO* __restrict__ out, int E, int F) {
   __shared__ float g[256];
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(256) moe_activate_kernel(const float* __restri
   for (int e = threadIdx.x; e < E; e += blockDim.x) g[e] = weights[r * ldw + e];
   __syncthreads();
   const int EF = E * F;
-  const float* src = up + r * EF;
+  const float* src = up + r * EF * (GATED ? 2 : 1);
   TO* dst = out + r * EF;
   for (int e = 0; e < E; ++e) {
     const float w = g[e];
@@ -152,8 +156,13 @@ __global__ void __launch_bounds__(256) moe_activate_kernel(const float* __restri
       for (int j = threadIdx.x; j < F; j += blockDim.x) dst[e * F + j] = sb::narrow<TO>(0.0f);
     } else {
       for (int j = threadIdx.x; j < F; j += blockDim.x) {
-        const float z = fmaxf(folded(src + e * F + j, n_partials, partial_stride), 0.0f);
-        dst[e * F + j] = sb::narrow<TO>(w * (z * z));
+        if (GATED) {
+          const float g = folded(src + 2 * e * F + j, n_partials, partial_stride), u = folded(src + (2 * e + 1) * F + j, n_partials, partial_stride);
+          dst[e * F + j] = sb::narrow<TO>(w * ((g / (1.0f + expf(-g))) * u));
+        } else {
+          const float z = fmaxf(folded(src + e * F + j, n_partials, partial_stride), 0.0f);
+          dst[e * F + j] = sb::narrow<TO>(w * (z * z));
+        }
       }
     }
   }
@@ -181,31 +190,41 @@ SB_EXPORT int sb_polynorm(const float* up, int n_partials, int64_t partial_strid
   return sb::check_launch("sb_polynorm");
 }
 
+// biased 0: softmax over all experts, chosen by score + correction, weights = the chosen scores normalised; 1: see moe_route_kernel.
 SB_EXPORT int sb_moe_route(const float* logits, int ldz, const void* correction, int correction_dtype, float* weights, int n, int X, int top,
-                           float scale, cudaStream_t stream) {
+                           float scale, int biased, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (X <= 0 || X > 256 || top <= 0 || top > X) return sb::fail("sb_moe_route: %d experts (at most 256), %d chosen", X, top);
   const int blocks = (n + 3) / 4;
-  if (correction_dtype == 0)
-    sb::launch_pdl(moe_route_kernel<float>, dim3(blocks), dim3(128), 0, stream, logits, ldz, static_cast<const float*>(correction), weights, n, X, top, scale);
-  else if (correction_dtype == 1)
-    sb::launch_pdl(moe_route_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, logits, ldz, static_cast<const bf16*>(correction), weights, n, X, top, scale);
-  else
+#define SB_ROUTE(TC, B) sb::launch_pdl(moe_route_kernel<TC, B>, dim3(blocks), dim3(128), 0, stream, logits, ldz, static_cast<const TC*>(correction), weights, n, X, top, scale)
+  if (correction_dtype == 0) {
+    if (biased) SB_ROUTE(float, true);
+    else SB_ROUTE(float, false);
+  } else if (correction_dtype == 1) {
+    if (biased) SB_ROUTE(bf16, true);
+    else SB_ROUTE(bf16, false);
+  } else
+#undef SB_ROUTE
     return sb::fail("sb_moe_route: unsupported correction dtype %d", correction_dtype);
   return sb::check_launch("sb_moe_route");
 }
 
-// out [n][E F] = weights[r, e] * relu(up)^2, up [P][n][E F] float32 partial sums, weights [n][ldw] (the first E columns).
+// out [n][E F] = weights[r, e] * relu(up)^2, up [P][n][E F] float32 partial sums, weights [n][ldw] (the first E columns);
+// gated: weights[r, e] * silu(gate) * up, up [P][n][E 2 F] with an expert's gate rows in front of its up rows.
 SB_EXPORT int sb_moe_activate(const float* up, int n_partials, int64_t partial_stride, const float* weights, int ldw, void* out, int out_dtype,
-                              int n, int E, int F, cudaStream_t stream) {
+                              int n, int E, int F, int gated, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n_partials < 1 || E <= 0 || F <= 0) return sb::fail("sb_moe_activate: n_partials %d, %d experts of %d", n_partials, E, F);
   if (E > 256) return sb::fail("sb_moe_activate: %d experts (at most 256)", E);
-  if (out_dtype == 0)
-    sb::launch_pdl(moe_activate_kernel<float>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<float*>(out), E, F);
-  else if (out_dtype == 1)
-    sb::launch_pdl(moe_activate_kernel<bf16>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<bf16*>(out), E, F);
-  else
+#define SB_ACT(TO, G) sb::launch_pdl(moe_activate_kernel<TO, G>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<TO*>(out), E, F)
+  if (out_dtype == 0) {
+    if (gated) SB_ACT(float, true);
+    else SB_ACT(float, false);
+  } else if (out_dtype == 1) {
+    if (gated) SB_ACT(bf16, true);
+    else SB_ACT(bf16, false);
+  } else
+#undef SB_ACT
     return sb::fail("sb_moe_activate: unsupported output dtype %d", out_dtype);
   return sb::check_launch("sb_moe_activate");
 }
@@ -224,19 +243,20 @@ SB_EXPORT int sb_op_polynorm(const SbOp* op, const SbStep* s, void* stream) {
                      (int)op->i[4], s->n, F, (float)op->f[0], (float)op->f[1], (float)op->f[2], (float)op->f[3], eps, static_cast<cudaStream_t>(stream));
 }
 
-// i: 0 logits, 1 ldz, 2 correction, 3 its dtype, 4 weights, 5 X, 6 top      f: 0 scale
+// i: 0 logits, 1 ldz, 2 correction, 3 its dtype, 4 weights, 5 X, 6 top, 7 biased      f: 0 scale
 SB_EXPORT int sb_op_moe_route(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
   return sb_moe_route(ptr<const float>(op->i[0]), (int)op->i[1], ptr<const void>(op->i[2]), (int)op->i[3], ptr<float>(op->i[4]), s->n, (int)op->i[5],
-                      (int)op->i[6], (float)op->f[0], static_cast<cudaStream_t>(stream));
+                      (int)op->i[6], (float)op->f[0], (int)op->i[7], static_cast<cudaStream_t>(stream));
 }
 
-// i: 0 up partial sums (flat), 1 K ranges S, 2 most tokens with a buffer per range, 3 weights, 4 ldw, 5 out, 6 out dtype, 7 E, 8 F
+// i: 0 up partial sums (flat), 1 K ranges S, 2 most tokens with a buffer per range, 3 weights, 4 ldw, 5 out, 6 out dtype, 7 E, 8 F, 9 gated
 SB_EXPORT int sb_op_moe_activate(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
-  const int E = (int)op->i[7], F = (int)op->i[8];
-  return sb_moe_activate(ptr<const float>(op->i[0]), partial_count(op->i[1], op->i[2], s->n), static_cast<int64_t>(s->n) * E * F,
-                         ptr<const float>(op->i[3]), (int)op->i[4], ptr<void>(op->i[5]), (int)op->i[6], s->n, E, F, static_cast<cudaStream_t>(stream));
+  const int E = (int)op->i[7], F = (int)op->i[8], gated = (int)op->i[9];
+  return sb_moe_activate(ptr<const float>(op->i[0]), partial_count(op->i[1], op->i[2], s->n), static_cast<int64_t>(s->n) * E * F * (gated ? 2 : 1),
+                         ptr<const float>(op->i[3]), (int)op->i[4], ptr<void>(op->i[5]), (int)op->i[6], s->n, E, F, gated,
+                         static_cast<cudaStream_t>(stream));
 }

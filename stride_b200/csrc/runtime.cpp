@@ -36,11 +36,13 @@ uint64_t splitmix64(uint64_t& s) {
 
 struct Group {
   int window = 0;
+  int keep = 0;                        // with a window: the first `keep` tokens of a request stay seen, so their pages are never given back
   int num_pages = 0;
   int32_t* table = nullptr;            // [max_slots + 1, max_pages_per_seq], kNoPage where nothing is held
   std::vector<int32_t> free;           // back = next page handed out
   std::vector<int32_t> first, last;    // per slot: the indices [first, last) are the only ones that can hold a page
   std::vector<int32_t> count;          // per slot: pages held
+  std::vector<int32_t> behind;         // per slot, groups that keep first tokens: the indices in front of this one have been looked at by trim
 };
 
 struct Pool {
@@ -119,8 +121,20 @@ SB_API void* sb_pool_create(int n_groups, const int32_t* windows, int32_t* const
     g.first.assign(max_slots, 0);
     g.last.assign(max_slots, 0);
     g.count.assign(max_slots, 0);
+    g.behind.assign(max_slots, 0);
   }
   return p;
+}
+
+// The first `keep` tokens of every request stay in group `group` whatever its window. Called before any slot is taken. 0, or -1.
+SB_API int sb_pool_set_keep(void* pool, int group, int keep) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (group < 0 || group >= (int)p->groups.size() || keep < 0) {
+    g_error = "sb_pool_set_keep: no such group, or a negative count";
+    return -1;
+  }
+  p->groups[group].keep = keep;
+  return 0;
 }
 
 SB_API void sb_pool_destroy(void* pool) { delete static_cast<Pool*>(pool); }
@@ -149,7 +163,7 @@ SB_API int sb_pool_release_slot(void* pool, int slot) {
         g.free.push_back(r[i]);
         r[i] = kNoPage;
       }
-    g.count[slot] = g.first[slot] = g.last[slot] = 0;
+    g.count[slot] = g.first[slot] = g.last[slot] = g.behind[slot] = 0;
     p->touch((int)gi, slot);
     if (p->shuffle) p->reshuffle(g);
   }
@@ -238,15 +252,20 @@ SB_API int sb_pool_trim(void* pool, int slot, int length) {
     const int keep_from = first_needed / p->page_size;    // index i goes when (i + 1) * page_size <= first_needed
     int32_t* r = p->row(g, slot);
     int here = 0;
-    for (int i = g.first[slot], e = std::min(keep_from, g.last[slot]); i < e; ++i)
+    // pages with kept first tokens stay, and so does `first`; `behind` then remembers how far earlier calls came
+    const int kept_pages = (g.keep + p->page_size - 1) / p->page_size;
+    const int from = kept_pages ? std::max(g.first[slot], std::max(kept_pages, g.behind[slot])) : g.first[slot];
+    const int to = std::min(keep_from, g.last[slot]);
+    for (int i = from; i < to; ++i)
       if (r[i] != kNoPage) {
         g.free.push_back(r[i]);
         r[i] = kNoPage;
         ++here;
       }
+    if (kept_pages) g.behind[slot] = std::max(g.behind[slot], to);
     if (here) {
       g.count[slot] -= here;
-      g.first[slot] = std::max(g.first[slot], std::min(keep_from, g.last[slot]));
+      if (!kept_pages) g.first[slot] = std::max(g.first[slot], to);
       p->touch((int)gi, slot);
       freed += here;
     }

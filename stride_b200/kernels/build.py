@@ -46,6 +46,7 @@ SOURCES = {
     "branch": "branch.cu",
     "feed_forward": "feed_forward.cu",
     "sigmoid_attention": "sigmoid_attention.cu",
+    "masked_attention": "masked_attention.cu",
     "gated_recurrence": "gated_recurrence.cu",
     "rglru": "rglru.cu",
     "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions

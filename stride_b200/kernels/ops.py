@@ -66,14 +66,15 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, slots=None, sampled=None, copy=None) -> None:
-    """out[i, :] = float32(table[tokens[i], :]); a token of -1 means sampled[slots[i]] (the request's last sampled token).
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, slots=None, sampled=None, copy=None, scale: float = 1.0) -> None:
+    """out[i, :] = float32(table[tokens[i], :]) * scale; a token of -1 means sampled[slots[i]] (the request's last sampled token).
     `copy` (float32, the shape of out) receives the same rows."""
     _cuda(tokens, table, out, slots, sampled, copy)
-    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                              c_void_p])
     n, H = out.shape
     _check(lib, fn(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out), n, H, table.shape[0], _ptr(slots),
-                   _ptr(sampled) if slots is not None else 0, _ptr(copy), _stream()))
+                   _ptr(sampled) if slots is not None else 0, _ptr(copy), scale, _stream()))
 
 
 def layernorm(h: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor, partials=None) -> None:
@@ -430,6 +431,27 @@ def branch_fold(dst: torch.Tensor, a=None, a_partials=None, ca: float = 1.0, b=N
                    n, W, _stream()))
 
 
+def branch_norm_fold(dst: torch.Tensor, gain, eps: float, a=None, a_partials=None, ca: float = 1.0, b=None, b_partials=None, cb: float = 1.0) -> None:
+    """y = ca * (a + sum of a_partials) + cb * (b + sum of b_partials); dst += gain * y / sqrt(mean(y^2) + eps) per row; a and b are zero afterwards."""
+    _cuda(dst, a, a_partials, b, b_partials, gain)
+    lib, fn = _fn("branch", "sb_branch_norm_fold", [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_float, c_void_p, c_void_p, c_int, c_int64, c_float,
+                                                    c_void_p, c_int, c_float, c_int, c_int, c_void_p])
+    n, W = dst.shape
+    pa, na, sa = _partials(a_partials)
+    pb, nb, sb = _partials(b_partials)
+    _check(lib, fn(_ptr(dst), _ptr(a), pa, na, sa, ca, _ptr(b), pb, nb, sb, cb, _ptr(gain), dtype_code(gain.dtype) if gain is not None else 0,
+                   eps, n, W, _stream()))
+
+
+def stream_add(dst: torch.Tensor, other=None, vector=None, partials=None) -> None:
+    """dst[r, :] = ((dst[r, :] + sum of partials) + other[r, :]) + vector[:], float32 rows; `other`, `vector` and `partials` may be None."""
+    _cuda(dst, other, vector, partials)
+    lib, fn = _fn("branch", "sb_stream_add", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    n, W = dst.shape
+    p, P, stride = _partials(partials)
+    _check(lib, fn(_ptr(dst), p, P, stride, _ptr(other), _ptr(vector), dtype_code(vector.dtype) if vector is not None else 0, n, W, _stream()))
+
+
 def row_scaled_add(dst: torch.Tensor, x: torch.Tensor, weights: torch.Tensor, first: int, count: int) -> None:
     """dst[r, :] += (weights[r, first] + .. + weights[r, first + count - 1]) * x[r, :]."""
     _cuda(dst, x, weights)
@@ -449,21 +471,26 @@ def polynorm(up: torch.Tensor, out: torch.Tensor, coefficients, eps: float) -> N
     _check(lib, fn(p, P, stride, _ptr(out), dtype_code(out.dtype), n, F, a, b, c, e, eps, _stream()))
 
 
-def moe_route(logits: torch.Tensor, correction: torch.Tensor, weights: torch.Tensor, top: int, scale: float) -> None:
+def moe_route(logits: torch.Tensor, correction: torch.Tensor, weights: torch.Tensor, top: int, scale: float, biased: bool = False) -> None:
     """weights[r, x] = softmax(logits[r])[x] / (sum over the chosen + 1e-20) * scale for the `top` experts with the largest
-    softmax + correction, 0 for the others."""
+    softmax + correction, 0 for the others. `biased`: the correction is the router's bias; the experts with the largest
+    logits + bias are chosen and weigh by the softmax over those alone (times scale)."""
     _cuda(logits, correction, weights)
-    lib, fn = _fn("feed_forward", "sb_moe_route", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    lib, fn = _fn("feed_forward", "sb_moe_route", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
     n, X = weights.shape
-    _check(lib, fn(_ptr(logits), logits.stride(0), _ptr(correction), dtype_code(correction.dtype), _ptr(weights), n, X, top, scale, _stream()))
+    _check(lib, fn(_ptr(logits), logits.stride(0), _ptr(correction), dtype_code(correction.dtype), _ptr(weights), n, X, top, scale, int(biased),
+                   _stream()))
 
 
-def moe_activate(up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, experts: int, ff: int) -> None:
-    """out[r, e ff + j] = weights[r, e] * relu(sum of up [P, n, E ff])^2."""
+def moe_activate(up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, experts: int, ff: int, gated: bool = False) -> None:
+    """out[r, e ff + j] = weights[r, e] * relu(sum of up [P, n, E ff])^2; `gated`: weights[r, e] * silu(gate) * up with
+    up [P, n, E 2 ff], an expert's ff gate rows in front of its ff up rows."""
     _cuda(up, weights, out)
-    lib, fn = _fn("feed_forward", "sb_moe_activate", [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    lib, fn = _fn("feed_forward", "sb_moe_activate", [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                      c_void_p])
     p, P, stride = _partials(up)
-    _check(lib, fn(p, P, stride, _ptr(weights), weights.stride(0), _ptr(out), dtype_code(out.dtype), out.shape[0], experts, ff, _stream()))
+    _check(lib, fn(p, P, stride, _ptr(weights), weights.stride(0), _ptr(out), dtype_code(out.dtype), out.shape[0], experts, ff, int(gated),
+                   _stream()))
 
 
 def qkv_rotate_append(qkv: torch.Tensor, positions, slots, cos_sin, rotary_dim: int, q_out, cache_layer, block_table, num_heads: int,
@@ -578,3 +605,103 @@ def rglru_scan(a, d, y, proj, x_bias, entry_meta: torch.Tensor, entries: int, st
     p, P, stride = _partials(proj)
     _check(lib, fn(_ptr(a), _ptr(d), _ptr(y), p, P, stride, _ptr(x_bias), dtype_code(x_bias.dtype), _ptr(entry_meta), entry_meta.stride(0), entries,
                    _ptr(state), _ptr(out), dtype_code(out.dtype), out.shape[1], taps, _stream()))
+
+
+# ---------------------------------------------------------------------------------------------- csrc/masked_attention.cu
+def _page_args(cache_layer, block_table):
+    """(pages, block table, pages per sequence, page size, page stride, value offset, head stride) of a `[pages, planes, Hkv, page_size, Dc]`
+    cache; with one plane the values lie in the key rows themselves (offset 0)."""
+    v_offset = cache_layer.stride(1) if cache_layer.shape[1] > 1 else 0
+    return [_ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0), v_offset, cache_layer.stride(2)]
+
+
+def qkv_norm_append(qkv: torch.Tensor, bias, q_gain, k_gain, eps: float, positions, slots, q_out, cache_layer, block_table, num_heads: int,
+                    num_kv_heads: int, key_dim: int, value_dim: int, write_kv: bool = True) -> None:
+    """qkv [P, n, Hq D + Hkv D + Hkv Dv] partial sums, + bias; the whole query projection RMS-normed times q_gain [Hq D], the whole key
+    projection times k_gain [Hkv D] (None: not normed); q stored, k and v appended to the pages. bias and gains float32."""
+    _cuda(qkv, bias, q_gain, k_gain, positions, slots, q_out, cache_layer, block_table)
+    lib, fn = _fn("masked_attention", "sb_qkv_norm_append",
+                  [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                   c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(qkv)
+    if q_out.dtype != cache_layer.dtype:
+        raise TypeError("qkv_norm_append takes q and cache of one dtype")
+    _check(lib, fn(p, P, stride, _ptr(bias), _ptr(q_gain), _ptr(k_gain), eps, _ptr(positions), _ptr(slots), _ptr(q_out), dtype_code(q_out.dtype),
+                   *_page_args(cache_layer, block_table), q_out.shape[0], num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4],
+                   int(write_kv), _stream()))
+
+
+def latent_prepare(proj: torch.Tensor, q_gain, kv_gain, eps: float, positions, slots, cos_sin, q_latent, cache_layer, block_table, q_rank: int,
+                   kv_rank: int, rot: int, write_kv: bool = True) -> None:
+    """proj [P, n, q_rank + kv_rank + rot] partial sums: both latents RMS-normed with their gains (float32), the query latent stored, the
+    key/value latent and the rotated last `rot` elements appended as one row [kv_rank | rot] of the token's page (one plane, one head)."""
+    _cuda(proj, q_gain, kv_gain, positions, slots, cos_sin, q_latent, cache_layer, block_table)
+    lib, fn = _fn("masked_attention", "sb_latent_prepare",
+                  [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                   c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(proj)
+    if q_latent.dtype != cache_layer.dtype:
+        raise TypeError("latent_prepare takes the query latent and the cache of one dtype")
+    _check(lib, fn(p, P, stride, _ptr(q_gain), _ptr(kv_gain), eps, _ptr(positions), _ptr(slots), _ptr(cos_sin), _ptr(q_latent),
+                   dtype_code(q_latent.dtype), _ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0),
+                   q_latent.shape[0], q_rank, kv_rank, rot, cache_layer.shape[4], int(write_kv), _stream()))
+
+
+def rotate_heads(q: torch.Tensor, positions, cos_sin, out: torch.Tensor, num_heads: int, head_dim: int, offset: int, rot: int) -> None:
+    """q [P, n, H D] partial sums -> out [n, H D]: elements offset .. offset + rot - 1 of every head rotated (pairs d, d + rot / 2)."""
+    _cuda(q, positions, cos_sin, out)
+    lib, fn = _fn("masked_attention", "sb_rotate_heads", [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                          c_int, c_void_p])
+    p, P, stride = _partials(q)
+    _check(lib, fn(p, P, stride, _ptr(positions), _ptr(cos_sin), _ptr(out), dtype_code(out.dtype), out.shape[0], num_heads, head_dim, offset, rot,
+                   _stream()))
+
+
+def masked_attention(q, out, cache_layer, block_table, positions, slots, slopes, sinks, num_heads: int, num_kv_heads: int, key_dim: int,
+                     value_dim: int, window: int, keep_first: int, scale: float) -> None:
+    """Softmax attention over the paged cache: score = scale q_i.k_j - slopes[h] (i - j); i sees j <= i with i - j < window or j < keep_first
+    (window 0: all); the denominator also holds exp(sinks[h]). slopes and sinks: float32 [H] or None."""
+    _cuda(q, out, cache_layer, block_table, positions, slots, slopes, sinks)
+    if not (q.dtype == out.dtype == cache_layer.dtype):
+        raise TypeError("masked_attention takes q, out and cache of one dtype")
+    lib, fn = _fn("masked_attention", "sb_masked_attention",
+                  [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), dtype_code(q.dtype), *_page_args(cache_layer, block_table), _ptr(positions), _ptr(slots), _ptr(slopes),
+                   _ptr(sinks), q.shape[0], num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4], window, keep_first, scale, _stream()))
+
+
+def masked_attention_tiles_supported(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, row: int, v_offset: int) -> bool:
+    """True if the tensor-core form of the masked attention takes this shape (bfloat16 only)."""
+    lib = library("masked_attention")
+    lib.sb_masked_attention_tiles_supported.argtypes = [c_int] * 5 + [c_int64]
+    lib.sb_masked_attention_tiles_supported.restype = c_int
+    return bool(lib.sb_masked_attention_tiles_supported(num_heads, num_kv_heads, key_dim, value_dim, row, v_offset))
+
+
+def masked_attention_tiles(q, out, cache_layer, block_table, entry_meta, entries: int, slopes, sinks, num_heads: int, num_kv_heads: int,
+                           key_dim: int, value_dim: int, window: int, keep_first: int, scale: float) -> None:
+    """`masked_attention` on the tensor cores (bfloat16 q, out and cache), entry by entry of the step."""
+    _cuda(q, out, cache_layer, block_table, entry_meta, slopes, sinks)
+    if not (q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16):
+        raise TypeError("masked_attention_tiles takes bfloat16 q, out and cache")
+    lib, fn = _fn("masked_attention", "sb_masked_attention_tiles",
+                  [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), *_page_args(cache_layer, block_table), _ptr(entry_meta), entry_meta.stride(0), entries, _ptr(slopes),
+                   _ptr(sinks), q.shape[0], num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4], window, keep_first, scale, _stream()))
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, tail: int = 0) -> None:
+    """out[r, h, :N] = weight[h]^T x[r, h, :K] (weight [H, K, N]); the `tail` elements of x behind the K are copied behind the N of out.
+    x [n, H, >= K + tail] and out [n, H, >= N + tail] may be views with any row and head strides; sums in 32-bit."""
+    _cuda(x, weight, out)
+    if not (x.dtype == weight.dtype == out.dtype):
+        raise TypeError("head_linear takes input, weights and output of one dtype")
+    H, K, N = weight.shape
+    if x.shape[1] != H or out.shape[1] != H or x.shape[2] < K + tail or out.shape[2] < N + tail or x.stride(2) != 1 or out.stride(2) != 1:
+        raise ValueError(f"head_linear: {tuple(x.shape)} -> {tuple(out.shape)} through {tuple(weight.shape)} with a tail of {tail}")
+    lib, fn = _fn("masked_attention", "sb_head_linear", [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+                                                         c_int, c_int, c_int, c_void_p])
+    _check(lib, fn(_ptr(x), x.stride(0), x.stride(1), _ptr(weight), _ptr(out), out.stride(0), out.stride(1), dtype_code(x.dtype), x.shape[0], H, K, N,
+                   tail, _stream()))

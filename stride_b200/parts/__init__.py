@@ -2,8 +2,8 @@ from .base import (Block, BranchScale, BuildEnv, CacheNeed, FeedForward, Mixer, 
                    register_part)
 from .context import ResidualStream, StepContext, Workspace
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorPlan
-from . import (attention, block, branch, ends, experts, hgrn2, lightning, mlp, norm, parallel, reentry, rglru, rope,  # register the built-in kinds
-               sigmoid_attention)
+from . import (attention, block, branch, ends, experts, hgrn2, lightning, masked_attention, mlp, norm, parallel, reentry, rglru,  # register the
+               rope, sigmoid_attention)                                                                                       # built-in kinds
 from .model import DecoderModel
 
 __all__ = ["Block", "BranchScale", "BuildEnv", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Rewrite", "part_class",

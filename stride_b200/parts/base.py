@@ -75,9 +75,10 @@ class BuildEnv:
 class CacheNeed:
     """What a mixer asks of the cache manager for one schedule entry.
 
-    kind "pages": keys and values per token, `[2, kv_heads, page_size, head_dim]` per page
-    and layer; `window` > 0 means only the last `window` tokens are ever read, so older
-    pages may be given back. kind "state": `state_shape` elements of `state_dtype` per
+    kind "pages": keys and values per token, `[planes, kv_heads, page_size, head_dim]` per page
+    and layer (`planes` is 2, keys and values, unless the mixer keeps one row per token that serves as both: 1);
+    `window` > 0 means only the last `window` tokens are ever read, so older pages may be given back, except those of a request's first
+    `keep_first` tokens, which stay seen. kind "state": `state_shape` elements of `state_dtype` per
     request, zeroed when a request takes its slot.
     """
     kind: str
@@ -87,6 +88,8 @@ class CacheNeed:
     dtype: torch.dtype = torch.float32
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
+    planes: int = 2
+    keep_first: int = 0
 
 
 class Part:

@@ -6,7 +6,10 @@ h += w2 * feed_forward(norm(h)). The mixer and the feed-forward are the same par
 handed a branch, a `ResidualStream` over a float32 buffer that is zero between uses, instead of the stream, so their
 last projection adds into the branch or leaves its K ranges' partial sums pending on it; the scale then takes
 both into the stream in one pass (csrc/branch.cu) and leaves the branch zero again. A part that is several parts side by
-side may hand its members' branches over unfolded (`forward_sources` / `emit_sources`), so that one pass scales and adds them all."""
+side may hand its members' branches over unfolded (`forward_sources` / `emit_sources`), so that one pass scales and adds them all.
+
+"rmsnorm" (category "branch_scale" too): h += w * r / sqrt(mean(r^2) + eps), a norm on the sublayer's result, for designs that norm a
+sublayer on both sides; the same blocks, the same branches, one kernel that norms on the way."""
 from __future__ import annotations
 
 import torch
@@ -82,16 +85,58 @@ class LayerScale(BranchScale):
         emit_fold(program, sources, self.weight, self.size)
 
 
-def emit_fold(program, sources, gain, width: int) -> None:
-    """The operation that takes one or two branches (buffer or None, pending or None, constant) into the program's stream."""
+@register_part("branch_scale", "rmsnorm")
+class BranchRMSNorm(BranchScale):
+    """The sublayer's result joins the residual RMS-normed over its row, times a gain. params: size, eps, offset (0 by default: the stored
+    vector is the gain's distance from it). tensors: weight [size]."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size, self.eps = int(spec.params["size"]), float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
+        self.weight = None
+
+    def tensor_plan(self):
+        return {self.spec.tensors["weight"]: TensorPlan((self.size,), zero_mean=self.offset != 0.0)}
+
+    def bind(self, tensors):
+        self.weight = tensors[self.spec.tensors["weight"]].contiguous()
+        if self.offset != 0.0:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def kernel_libraries(self):
+        return {"branch"}
+
+    def forward(self, ctx, sources, stream):
+        """sources: one or two (Branch, constant)."""
+        stream.fold()
+        (a, pa), ca = sources[0][0].source(), sources[0][1]
+        (b, pb), cb = (sources[1][0].source(), sources[1][1]) if len(sources) > 1 else ((None, None), 1.0)
+        ops.branch_norm_fold(stream.h, self.weight, self.eps, a=a, a_partials=pa, ca=ca, b=b, b_partials=pb, cb=cb)
+
+    def emit(self, program, sources):
+        program.need_folded("a norm behind a sublayer")
+        emit_fold(program, sources, self.weight, self.size, norm_eps=self.eps)
+
+
+def emit_fold(program, sources, gain, width: int, norm_eps: float = None) -> None:
+    """The operation that takes one or two branches (buffer or None, pending or None, constant) into the program's stream; with
+    `norm_eps` their sum is RMS-normed over its row before the gain."""
     if not 1 <= len(sources) <= 2:
         raise ValueError("a fold takes one or two branches")
     (a, pa, ca), (b, pb, cb) = sources[0], sources[1] if len(sources) > 1 else (None, None, 1.0)
     (fa, Sa, _), (fb, Sb, _) = pa or (None, 1, 0), pb or (None, 1, 0)
     if a is None and fa is None:
         raise ValueError("a branch that nothing wrote into")
-    program.add("branch", "sb_op_branch_fold", [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, gain, gain.dtype if gain is not None else 0, width],
-                [ca, cb])
+    ints = [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, gain, gain.dtype if gain is not None else 0, width]
+    if norm_eps is None:
+        program.add("branch", "sb_op_branch_fold", ints, [ca, cb])
+    else:       # the branches' sum is RMS-normed over its row on the way
+        program.add("branch", "sb_op_branch_norm_fold", ints, [ca, cb, norm_eps])
 
 
 class _ScaledBlock(Block):

@@ -1,6 +1,6 @@
 """The two ends of a decoder: the token embedding and the output head.
 
-Embedding: h = widen(table[token]), no scaling (arhaamatiq/stride src/kernels.cu:98-116).
+Embedding: h = widen(table[token]) (arhaamatiq/stride src/kernels.cu:98-116), times a constant for designs that scale it.
 Head: logits = W x for the rows that want logits; W is `lm_head.weight` if the
 checkpoint has it, else the embedding table (src/model.cpp:228-232).
 """
@@ -16,7 +16,7 @@ from .spec import TensorPlan
 
 @register_part("embedding", "lookup")
 class Embedding(Part):
-    """params: vocab_size, hidden_size. tensors: weight."""
+    """params: vocab_size, hidden_size, scale (1 by default: a factor on every element, applied in 32-bit). tensors: weight."""
     graph_safe = True
 
 
@@ -24,6 +24,7 @@ class Embedding(Part):
         super().__init__(spec, env)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensor_plan(self):
@@ -37,10 +38,11 @@ class Embedding(Part):
 
     def forward(self, ctx, out, copy=None):
         """`copy`: a second buffer for the same rows, for models whose later layers read the embedding again."""
-        ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled, copy)
+        ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled, copy, self.scale)
 
     def emit(self, program, out, sampled, copy=None):
-        program.add("elementwise", "sb_op_embed", [self.weight, self.weight.dtype, out, self.hidden, self.weight.shape[0], sampled, copy])
+        program.add("elementwise", "sb_op_embed", [self.weight, self.weight.dtype, out, self.hidden, self.weight.shape[0], sampled, copy],
+                    [self.scale])
 
 
 @register_part("head", "linear")

@@ -9,7 +9,11 @@ experts; the `top` experts with the largest s + correction are chosen; a chosen 
 s + 1e-20) * scale. The experts' up matrices lie side by side as one matrix, so do the down matrices: the hidden
 activations of experts that a token did not choose are exact zeros (times weight 0), so one product each way is the
 weighted sum of the chosen experts; identity experts add their weight times x. Kernels between the products:
-csrc/feed_forward.cu; the identity experts' share: csrc/branch.cu."""
+csrc/feed_forward.cu; the identity experts' share: csrc/branch.cu.
+
+Two parameters make other routed designs of it. `weights_from` "logits": the stored vector is the router's bias, z = W_r x + b, the
+`top` largest z are chosen and weigh by the softmax over the chosen z alone. `expert` "silu_gated": an expert is
+W_down (silu(W_gate x) * (W_up x)); its gate and up matrices lie one above the other in the side-by-side product."""
 from __future__ import annotations
 
 import torch
@@ -70,8 +74,9 @@ class PolyNormFeedForward(FeedForward):
 @register_part("feed_forward", "routed")
 class RoutedFeedForward(FeedForward):
     """params: hidden_size, intermediate_size (of one expert), experts, identity (experts without weights, listed last by the
-    router), top, scale. tensors: router [experts + identity, hidden], correction [experts + identity], up and down (lists of
-    names, one per expert)."""
+    router), top, scale (1 by default), weights_from ("scores" by default, or "logits"), expert ("relu2" by default, or "silu_gated").
+    tensors: router [experts + identity, hidden], correction [experts + identity], up and down (lists of names, one per expert), gate
+    (the same, for gated experts)."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -79,7 +84,9 @@ class RoutedFeedForward(FeedForward):
         p = spec.params
         self.hidden, self.intermediate = int(p["hidden_size"]), int(p["intermediate_size"])
         self.experts, self.identity, self.top = int(p["experts"]), int(p.get("identity", 0)), int(p["top"])
-        self.scale = float(p["scale"])
+        self.scale = float(p.get("scale", 1.0))
+        self.biased = {"scores": False, "logits": True}[p.get("weights_from", "scores")]
+        self.gated = {"relu2": False, "silu_gated": True}[p.get("expert", "relu2")]
         self.outputs = self.experts + self.identity
         if not 0 < self.top <= self.outputs or self.outputs > 256:
             raise ValueError(f"routed feed-forward: {self.top} of {self.outputs} experts (at most 256)")
@@ -88,7 +95,7 @@ class RoutedFeedForward(FeedForward):
     def tensor_plan(self):
         t = self.spec.tensors
         plan = {t["router"]: TensorPlan((self.outputs, self.hidden)), t["correction"]: TensorPlan((self.outputs,), zero_mean=True)}
-        for name in t["up"]:
+        for name in (*t["up"], *(t["gate"] if self.gated else ())):
             plan[name] = TensorPlan((self.intermediate, self.hidden))
         for name in t["down"]:
             plan[name] = TensorPlan((self.hidden, self.intermediate))
@@ -106,7 +113,8 @@ class RoutedFeedForward(FeedForward):
         self.router = tensors[t["router"]].contiguous()
         self.correction = tensors[t["correction"]].to(torch.float32).contiguous()
         if self.experts:
-            self.up = Linear(side_by_side(t["up"], 0), self.env.compute_dtype)
+            rows = t["up"] if not self.gated else [name for pair in zip(t["gate"], t["up"]) for name in pair]
+            self.up = Linear(side_by_side(rows, 0), self.env.compute_dtype)
             self.down = Linear(side_by_side(t["down"], 1), self.env.compute_dtype)
 
     def weight_bytes(self):
@@ -121,14 +129,14 @@ class RoutedFeedForward(FeedForward):
         logits = ws.get("routed.logits", n, (self.outputs,), torch.float32)
         ops.gemm_f32(x, self.router, logits)
         weights = ws.get("routed.weights", n, (self.outputs,), torch.float32)
-        ops.moe_route(logits, self.correction, weights, self.top, self.scale)
+        ops.moe_route(logits, self.correction, weights, self.top, self.scale, self.biased)
         if self.identity:
             stream.fold()
             ops.row_scaled_add(stream.h, x, weights, E, self.identity)
         if E:
             up = self.up.forward_partials(x, ws.raw("routed.up", (self.up.partial_elems(ws.max_tokens),), torch.float32))
             z = ws.get("routed.z", n, (E * F,), ctx.act_dtype)
-            ops.moe_activate(up, weights, z, E, F)
+            ops.moe_activate(up, weights, z, E, F, self.gated)
             self.down.forward_add(z, stream, ws.raw("routed.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))
 
     def emit(self, program, x):
@@ -138,7 +146,8 @@ class RoutedFeedForward(FeedForward):
         program.add("gemm_f32", "sb_op_linear_f32", [x, x.dtype, x.stride(0), self.router, self.router.dtype, self.router.stride(0), logits, X, X,
                                                      self.hidden, 0, 0])
         weights = ws.get("routed.weights", T, (X,), f32)
-        program.add("feed_forward", "sb_op_moe_route", [logits, X, self.correction, self.correction.dtype, weights, X, self.top], [self.scale])
+        program.add("feed_forward", "sb_op_moe_route", [logits, X, self.correction, self.correction.dtype, weights, X, self.top, int(self.biased)],
+                    [self.scale])
         if self.identity:
             program.need_folded("identity experts")
             program.add("branch", "sb_op_row_scaled_add", [program.h, x, x.dtype, weights, X, E, self.identity, self.hidden])
@@ -146,5 +155,5 @@ class RoutedFeedForward(FeedForward):
             up = ws.raw("routed.up", (self.up.partial_elems(T),), f32)
             S = self.up.emit_partials(program, x, up)
             z = ws.get("routed.z", T, (E * F,), self.env.act_dtype)
-            program.add("feed_forward", "sb_op_moe_activate", [up, S, program.few_tokens, weights, X, z, z.dtype, E, F])
+            program.add("feed_forward", "sb_op_moe_activate", [up, S, program.few_tokens, weights, X, z, z.dtype, E, F, int(self.gated)])
             self.down.emit_add(program, z, ws.raw("routed.down_partials", (self.down.partial_elems(T),), f32))

@@ -40,11 +40,33 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: dict) -> np.ndar
     return inv
 
 
+def yarn_frequencies(rotary_dim: int, theta: float, factor: float, original: float, fast: float, slow: float):
+    """YaRN: pairs that complete more than `fast` turns over `original` positions keep their frequency, pairs that complete fewer than
+    `slow` turns are slowed by `factor`, and in between a ramp over the pair index blends the two. Pair i of frequency
+    f_i = theta^(-2i/d) completes `t` turns at index d ln(original / (2 pi t)) / (2 ln theta). Returns (frequencies in 64-bit, the
+    factor 0.1 ln(factor) + 1 that cos and sin are multiplied by)."""
+    half = rotary_dim // 2
+
+    def index_of(turns):
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), rotary_dim - 1)
+    inv = np.empty(half, dtype=np.float64)
+    for i in range(half):
+        f = math.pow(theta, -2.0 * i / rotary_dim)
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        inv[i] = f / factor * ramp + f * (1.0 - ramp)
+    return inv, 0.1 * math.log(factor) + 1.0
+
+
 @register_part("position", "rope")
 class RotaryEncoding(PositionEncoding):
     """params: head_dim, rotary_dim (default head_dim), theta, scaling (dict with rope_type and its factors),
     exact_angles (False by default: frequencies and angles in 32-bit as above; True: frequency theta^(-2i/rotary_dim) and
-    angle in 64-bit, so that the table is the rounding of the exact cos and sin at every position)."""
+    angle in 64-bit, so that the table is the rounding of the exact cos and sin at every position). The scaling
+    {"rope_type": "yarn", factor, original, fast, slow} (`yarn_frequencies`) is always made in 64-bit, and its factor on cos and sin
+    is part of the table."""
     graph_safe = True
 
 
@@ -55,7 +77,13 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(p.get("rotary_dim", self.head_dim))
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim or self.rotary_dim <= 0:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and in 2..head_dim {self.head_dim}")
-        if p.get("exact_angles"):
+        magnitude = 1.0
+        if (p.get("scaling") or {}).get("rope_type") == "yarn":
+            sc = p["scaling"]
+            inv, magnitude = yarn_frequencies(self.rotary_dim, float(p["theta"]), float(sc["factor"]), float(sc["original"]), float(sc["fast"]),
+                                              float(sc["slow"]))
+            angle = inv[None, :] * np.arange(env.max_positions, dtype=np.float64)[:, None]
+        elif p.get("exact_angles"):
             if (p.get("scaling") or {}).get("rope_type", "default") != "default":
                 raise ValueError("rotary encoding: exact_angles goes with the default scaling only")
             inv = np.array([math.pow(float(p["theta"]), -2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)], dtype=np.float64)
@@ -64,5 +92,5 @@ class RotaryEncoding(PositionEncoding):
             inv = inverse_frequencies(self.rotary_dim, float(p["theta"]), p.get("scaling") or {})
             pos = np.arange(env.max_positions, dtype=np.float32)
             angle = (inv[None, :] * pos[:, None]).astype(np.float32).astype(np.float64)
-        table = np.stack([np.cos(angle), np.sin(angle)], axis=-1).astype(np.float32)
+        table = (np.stack([np.cos(angle), np.sin(angle)], axis=-1) * magnitude).astype(np.float32)
         self.cos_sin = torch.from_numpy(table).to(env.device)   # [max_positions, rotary_dim / 2, 2]
