@@ -354,6 +354,19 @@ def _ganupel_config(width: int, ff: int, vocab: int, pairs: int, window: int) ->
     return {"architecture": "Ganupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": [rec, par] * pairs}
 
 
+def _pusisun_config(width: int, ff: int, vocab: int, pairs: int, window: int) -> dict:
+    """`pairs` times (masked attention, latent attention), each with routed gated experts: the attention has the heads of the Llama
+    3.2 1B layer, a window that keeps the first four tokens, slopes and a sink; the latent attention 16 heads of 128 unrotated and 64
+    rotated elements over a latent of 512 (a cached row of 576), queries through a latent of 768; eight experts of ff / 4, two chosen."""
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "top": 2}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": window, "keep_first": 4}}}
+    lat = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"heads": width // 128, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512, "scale": 192 ** -0.5,
+                     "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Pusisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": [att, lat] * pairs}
+
+
 def design_compare(a) -> int:
     """Keralorn at layer sizes of a real model beside LlamaForCausalLM with as many layers of the same width, heads and
     feed-forward (random weights, bfloat16 engine): a prompt of 2,048 tokens in one step, decode steps at batch 8 and 64
@@ -370,8 +383,10 @@ def design_compare(a) -> int:
     configs = {"keralorn": _keralorn_config(width, ff, vocab, pairs, 1024), "llama": llama}
     if a.design == "ganupel":      # beside the closest design (a recurrence with a state per request and windowed attention) and Llama
         configs = {"ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), **configs}
+    if a.design == "pusisun":      # beside the closest design (windowed attention of the same heads, routed experts of the same sizes) and Llama
+        configs = {"pusisun": _pusisun_config(width, ff, vocab, pairs, 1024), "ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), "llama": llama}
     gen = torch.Generator().manual_seed(3)
-    out = {"design": a.design, "beside": "LlamaForCausalLM" if a.design == "keralorn" else "Keralorn, LlamaForCausalLM", "width": width, "ff": ff, "layers": layers, "vocab": vocab,
+    out = {"design": a.design, "beside": {"keralorn": "LlamaForCausalLM", "ganupel": "Keralorn, LlamaForCausalLM", "pusisun": "Ganupel, LlamaForCausalLM"}[a.design], "width": width, "ff": ff, "layers": layers, "vocab": vocab,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": pk,
            "l2": "weights and caches of a step exceed the 126 MB L2; the kernel timings flush L2 between launches"}
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
@@ -449,8 +464,8 @@ def design_compare(a) -> int:
         del eng
         torch.cuda.empty_cache()
 
-    if a.design == "ganupel":
-        out["kernels"] = _ganupel_kernels(timed, pk, width, ff)
+    if a.design in ("ganupel", "pusisun"):
+        out["kernels"] = (_ganupel_kernels if a.design == "ganupel" else _pusisun_kernels)(timed, pk, width, ff)
         out["clocks"] = clocks.stop()
         print(json.dumps(out))
         return 0
@@ -608,6 +623,125 @@ def _ganupel_kernels(timed, pk: dict, width: int, ff: int) -> dict:
     return kern
 
 
+def _pusisun_kernels(timed, pk: dict, width: int, ff: int) -> dict:
+    """Pusisun's own kernels alone (L2 flushed between launches), each beside the like kernel of Ganupel or Llama."""
+    import torch
+    from stride_b200.kernels import ops
+    dev, kern = "cuda", {}
+    hbm = pk["hbm_gbs"] * 1e9
+
+    def record(label, ms, moved=None, flops=None, **more):
+        r = {"ms": round(ms, 4)}
+        if moved is not None:
+            r.update(gb_s=round(moved / ms / 1e6, 1), hbm_fraction_of_measured=round(moved / (ms * 1e-3) / hbm, 3))
+        if flops is not None:
+            r.update(tflops=round(flops / ms / 1e9, 2), fraction_of_measured_bf16=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+        r.update(more)
+        kern[label] = r
+
+    def paged(entries, length, past, G, row, planes, page=64):
+        n, per = entries * length, (past + length + page - 1) // page
+        pages = torch.randn(entries * per + 1, planes, G, page, row, device=dev).to(torch.bfloat16)
+        table = torch.arange(entries * per, dtype=torch.int32, device=dev).view(entries, per)
+        pos = torch.tensor([past + t for _ in range(entries) for t in range(length)], dtype=torch.int32, device=dev)
+        slot = torch.tensor([e for e in range(entries) for _ in range(length)], dtype=torch.int32, device=dev)
+        meta = torch.tensor([list(range(entries)), [e * length for e in range(entries)], [length] * entries, [past] * entries],
+                            dtype=torch.int32, device=dev)
+        return n, pages, table, pos, slot, meta
+
+    # masked attention beside the sigmoid attention of Ganupel: the same heads, window and pages
+    Hq, G, Dh, window, keep = width // 64, width // 256, 64, 1024, 4
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / Hq) for h in range(Hq)], device=dev)
+    sinks = torch.zeros(Hq, device=dev)
+    for label, entries, length, past in (("prefill_2048", 1, 2048, 0), ("decode_b64", 64, 1, 1500)):
+        n, pages, table, pos, slot, meta = paged(entries, length, past, G, Dh, 2)
+        q = torch.randn(n, Hq * Dh, device=dev).to(torch.bfloat16)
+        o = torch.empty_like(q)
+        seen = lambda i: min(window, i + 1) + min(keep, max(i + 1 - window, 0))
+        keys = sum(seen(past + t) for t in range(length)) * entries
+        moved = (2.0 * entries * G * seen(past) * Dh * 2 + n * Hq * Dh * 4) if length == 1 else None
+        ms = timed(lambda: ops.masked_attention_tiles(q, o, pages, table, meta, entries, slopes, sinks, Hq, G, Dh, Dh, window, keep, 0.125), 5, clear=True)
+        record("masked_attention_" + label, ms, moved, 4.0 * keys * Hq * Dh)
+        ms = timed(lambda: ops.sigmoid_attention_tiles(q, o, pages, table, meta, entries, sinks, Hq, G, Dh, Dh, window, 0.125), 5, clear=True)
+        keys_s = sum(min(window, past + t + 1) for t in range(length)) * entries
+        record("ganupel_sigmoid_attention_" + label, ms, moved, 6.0 * keys_s * Hq * Dh)       # its weights go through the tensor cores as two parts
+        ms = timed(lambda: ops.masked_attention(q, o, pages, table, pos, slot, slopes, sinks, Hq, G, Dh, Dh, window, keep, 0.125), 3, clear=True)
+        record("masked_attention_block_per_token_" + label, ms, moved, 4.0 * keys * Hq * Dh)
+    # latent attention: every earlier key, one cached row of 576 per token read by all 16 heads, the values its first 512 elements
+    H, D, R, V, C, Q = width // 128, 128, 64, 128, 512, 768
+    row = C + R
+    cs = torch.rand(4096, R // 2, 2, device=dev)
+    for label, entries, length, past in (("prefill_2048", 1, 2048, 0), ("decode_b64", 64, 1, 1500)):
+        n, pages, table, pos, slot, meta = paged(entries, length, past, 1, row, 1)
+        ql = torch.randn(n, H * row, device=dev).to(torch.bfloat16)
+        ol = torch.empty(n, H * C, dtype=torch.bfloat16, device=dev)
+        keys = sum(past + t + 1 for t in range(length)) * entries
+        moved = (entries * (past + 1) * row * 2.0 + n * H * (row + C) * 2.0) if length == 1 else None
+        ms = timed(lambda: ops.masked_attention_tiles(ql, ol, pages, table, meta, entries, None, None, H, 1, row, C, 0, 0, 0.07), 5, clear=True)
+        record("latent_attention_" + label, ms, moved, 2.0 * keys * H * (row + C))
+    # the kernels in front of and behind the attentions, for a prompt of 2,048 tokens and for 64 decoded tokens
+    for n in (2048, 64):
+        entries = 1 if n == 2048 else n
+        length, past = (n, 0) if entries == 1 else (1, 9)
+        _, pages, table, pos, slot, meta = paged(entries, length, past, G, Dh, 2)
+        wq = Hq * Dh + 2 * G * Dh
+        qkv = torch.randn(1, n, wq, device=dev)
+        bias, qg, kg = torch.randn(wq, device=dev), torch.ones(Hq * Dh, device=dev), torch.ones(G * Dh, device=dev)
+        q = torch.empty(n, Hq * Dh, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.qkv_norm_append(qkv, bias, qg, kg, 1e-6, pos, slot, q, pages, table, Hq, G, Dh, Dh), 5, clear=True)
+        record(f"qkv_norm_append_{n}", ms, n * wq * 6.0)
+        csr = torch.rand(4096, Dh // 2, 2, device=dev)
+        ms = timed(lambda: ops.qkv_rotate_append(qkv, pos, slot, csr, Dh, q, pages, table, Hq, G, Dh, Dh), 5, clear=True)
+        record(f"ganupel_qkv_rotate_append_{n}", ms, n * wq * 6.0)
+        _, lpages, ltable, pos, slot, meta = paged(entries, length, past, 1, row, 1)
+        proj = torch.randn(1, n, Q + row, device=dev)
+        cq = torch.empty(n, Q, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.latent_prepare(proj, torch.ones(Q, device=dev), torch.ones(C, device=dev), 1e-6, pos, slot, cs, cq, lpages, ltable, Q, C, R),
+                   5, clear=True)
+        record(f"latent_prepare_{n}", ms, n * (Q + row) * 6.0)
+        qp = torch.randn(1, n, H * (D + R), device=dev)
+        qh = torch.empty(n, H, D + R, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.rotate_heads(qp, pos, cs, qh.view(n, H * (D + R)), H, D + R, D, R), 5, clear=True)
+        record(f"rotate_heads_{n}", ms, n * H * (D + R) * 6.0)
+        uk = (torch.randn(H, D, C, device=dev) * 0.05).to(torch.bfloat16)
+        uv = (torch.randn(H, C, V, device=dev) * 0.05).to(torch.bfloat16)
+        ql = torch.empty(n, H, row, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.head_linear(qh, uk, ql, tail=R), 5, clear=True)
+        record(f"head_linear_keys_into_queries_{n}", ms, n * H * (D + R + row) * 2.0 + uk.numel() * 2.0, 2.0 * n * H * D * C)
+        ol = torch.randn(n, H, C, device=dev).to(torch.bfloat16)
+        mixed = torch.empty(n, H, V, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.head_linear(ol, uv, mixed), 5, clear=True)
+        record(f"head_linear_values_{n}", ms, n * H * (C + V) * 2.0 + uv.numel() * 2.0, 2.0 * n * H * C * V)
+    # between the products of the feed-forward, and the norm behind a sublayer beside the plain fold and the norm in front
+    for n in (64, 2048):
+        E, F = 8, ff // 4
+        logits = torch.randn(n, E, device=dev)
+        w = torch.empty(n, E, device=dev)
+        rb = torch.zeros(E, device=dev)
+        ms = timed(lambda: ops.moe_route(logits, rb, w, 2, 1.0, biased=True), 5, clear=True)
+        record(f"moe_route_{n}", ms, n * E * 8.0)
+        upe = torch.randn(1, n, 2 * E * F, device=dev)
+        ze = torch.empty(n, E * F, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.moe_activate(upe, w, ze, E, F, gated=True), 5, clear=True)
+        record(f"moe_activate_gated_{n}", ms, n * E * F * 2.0 + n * 2 * 2 * F * 4.0)
+        up1 = torch.randn(1, n, E * F, device=dev)
+        ms = timed(lambda: ops.moe_activate(up1, w, ze, E, F), 5, clear=True)
+        record(f"ganupel_moe_activate_{n}", ms, n * E * F * 2.0 + n * 2 * F * 4.0)
+        h = torch.randn(n, width, device=dev)
+        br = torch.randn(n, width, device=dev)
+        parts = torch.randn(2, n, width, device=dev)
+        gain = torch.ones(width, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.branch_norm_fold(h, gain, 1e-6, a=br, a_partials=parts), 5, clear=True)
+        ms_f = timed(lambda: ops.branch_fold(h, a=br, a_partials=parts, gain=gain), 5, clear=True)
+        x = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+        ms_r = timed(lambda: ops.rmsnorm(h, gain, 1e-6, x, partials=parts), 5, clear=True)
+        record(f"branch_norm_fold_{n}", ms, n * width * 24.0, ganupel_branch_fold_ms=round(ms_f, 4), rmsnorm_with_two_partials_ms=round(ms_r, 4))
+        e = torch.randn(n, width, device=dev)
+        ms = timed(lambda: ops.stream_add(h, e, gain, partials=parts), 5, clear=True)
+        record(f"stream_add_{n}", ms, n * width * 20.0)
+    return kern
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -618,9 +752,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="1b: the decode step (default); 3b, 8b: serving runs")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64, float32 and prefill measurements")
-    ap.add_argument("--design", default="", choices=["", "keralorn", "ganupel"],
+    ap.add_argument("--design", default="", choices=["", "keralorn", "ganupel", "pusisun"],
                     help="keralorn: prefill and decode of that design beside a Llama of equal layer sizes, and its own kernels alone; "
-                         "ganupel: the same beside Keralorn and Llama")
+                         "ganupel: the same beside Keralorn and Llama; pusisun: the same beside Ganupel and Llama")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)

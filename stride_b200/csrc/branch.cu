@@ -111,17 +111,37 @@ __global__ void __launch_bounds__(256) branch_fold_kernel(float* __restrict__ ds
 }
 
 // A block per row: the row's values (the branches read and cleared as above) stay in shared memory between the sum of squares and the
-// scaled add. The squares are added by a thread in ascending columns, then over the block in `block_sum`'s order.
-template <class TG>
+// scaled add. The squares are added by a thread in ascending columns, then over the block in `block_sum`'s order. VEC: the width is a
+// multiple of four and every buffer 16-byte aligned: four elements a thread and request. Which form runs depends on the width and the
+// buffers alone, never on the rows of the step.
+template <class TG, bool VEC>
 __global__ void __launch_bounds__(256) branch_norm_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ gain, int W,
                                                                float eps) {
-  extern __shared__ float row_values[];
+  extern __shared__ __align__(16) float row_values[];
   __shared__ float red[32];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
   const bool two = b.h != nullptr || b.partials != nullptr;
   float sq = 0.0f;
+  if (VEC) {
+    float4* held = reinterpret_cast<float4*>(row_values);
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      const int64_t i = (row + c) / 4;
+      float4 v = mul(source_value<float4>(a, i), a.c);
+      if (two) v = add(v, mul(source_value<float4>(b, i), b.c));
+      held[c / 4] = v;
+      sq = fmaf(v.x, v.x, sq), sq = fmaf(v.y, v.y, sq), sq = fmaf(v.z, v.z, sq), sq = fmaf(v.w, v.w, sq);
+    }
+    const float scale = 1.0f / sqrtf(sb::block_sum(sq, red) / static_cast<float>(W) + eps);
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      float4 v = mul(held[c / 4], scale);
+      if (gain != nullptr) v = mul(v, gain4<TG>(gain, c));
+      float4* d = reinterpret_cast<float4*>(dst) + (row + c) / 4;
+      *d = add(*d, v);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     float v = mul(source_value<float>(a, row + c), a.c);
     if (two) v = add(v, mul(source_value<float>(b, row + c), b.c));
@@ -197,16 +217,24 @@ SB_EXPORT int sb_branch_norm_fold(float* dst, float* a, const float* pa, int na,
   const Source A{a, pa, pa ? na : 0, sa, ca}, B{b, pb, pb ? nb : 0, sb_, cb};
   const size_t smem = static_cast<size_t>(W) * sizeof(float);
   if (smem > 160 * 1024) return sb::fail("sb_branch_norm_fold: a row of %d elements does not fit the row buffer", W);
+  const bool vec = W % 4 == 0 && aligned16(dst) && aligned16(a) && aligned16(pa) && aligned16(b) && aligned16(pb) && aligned16(gain) &&
+                   sa % 4 == 0 && sb_ % 4 == 0;
   const int threads = W >= 1024 ? 256 : 128;
+#define SB_NORM_FOLD(TG, VEC)                                                                                                              \
+  do {                                                                                                                                     \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_norm_fold_kernel<TG, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    sb::launch_pdl(branch_norm_fold_kernel<TG, VEC>, dim3(n), dim3(threads), smem, stream, dst, A, B, static_cast<const TG*>(gain), W, eps); \
+  } while (0)
   if (gain == nullptr || gain_dtype == 0) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_norm_fold_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(branch_norm_fold_kernel<float>, dim3(n), dim3(threads), smem, stream, dst, A, B, static_cast<const float*>(gain), W, eps);
+    if (vec) SB_NORM_FOLD(float, true);
+    else SB_NORM_FOLD(float, false);
   } else if (gain_dtype == 1) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_norm_fold_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(branch_norm_fold_kernel<bf16>, dim3(n), dim3(threads), smem, stream, dst, A, B, static_cast<const bf16*>(gain), W, eps);
+    if (vec) SB_NORM_FOLD(bf16, true);
+    else SB_NORM_FOLD(bf16, false);
   } else {
     return sb::fail("sb_branch_norm_fold: unsupported gain dtype %d", gain_dtype);
   }
+#undef SB_NORM_FOLD
   return sb::check_launch("sb_branch_norm_fold");
 }
 

@@ -345,6 +345,80 @@ __device__ __forceinline__ void copy16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
 }
 
+// The matrix per head on the tensor cores (bfloat16, mma.sync.m16n8k16, float32 accumulation). A CTA of four warps makes 64 rows x 64
+// columns of one head; warp w owns rows 16 w .. 16 w + 15. K is walked in chunks of 64, staged twice over with cp.async: the rows' slice
+// [64][64] and the weights' slice [64 k][64 n], n contiguous as stored, read as the B operand through ldmatrix.trans. A row's sum runs
+// over k in ascending steps of 16 whatever its neighbours are, so a token has the same bits in a prompt, in a portion and decoded alone.
+constexpr int kHlTile = 64, kHlLd = kHlTile + 8;
+
+__global__ void __launch_bounds__(128) head_linear_tc_kernel(HeadLinearParams p) {
+  __shared__ __align__(16) bf16 As[2][kHlTile * kHlLd];
+  __shared__ __align__(16) bf16 Bs[2][kHlTile * kHlLd];
+  sb::grid_launch_dependents();
+  const int h = blockIdx.y, r0 = blockIdx.x * kHlTile, n0 = blockIdx.z * kHlTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bf16* in = static_cast<const bf16*>(p.in) + static_cast<int64_t>(h) * p.in_head;
+  bf16* out = static_cast<bf16*>(p.out) + static_cast<int64_t>(h) * p.out_head;
+  const bf16* w = static_cast<const bf16*>(p.w) + static_cast<int64_t>(h) * p.K * p.N;
+  sb::grid_dependency_wait();
+  auto request = [&](int kc, int buf) {
+    for (int i = threadIdx.x; i < kHlTile * 8; i += blockDim.x) {
+      const int r = i >> 3, c = (i & 7) * 8, k = kc * kHlTile + c;
+      bf16* a = &As[buf][r * kHlLd + c];
+      if (r0 + r < p.n && k < p.K) copy16(a, in + static_cast<int64_t>(r0 + r) * p.in_row + k);
+      else *reinterpret_cast<uint4*>(a) = make_uint4(0, 0, 0, 0);
+      bf16* b = &Bs[buf][r * kHlLd + c];                       // here r is the k of the chunk and c the column of the slice
+      if (kc * kHlTile + r < p.K && n0 + c < p.N) copy16(b, w + static_cast<int64_t>(kc * kHlTile + r) * p.N + n0 + c);
+      else *reinterpret_cast<uint4*>(b) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (blockIdx.z == 0)
+    for (int i = threadIdx.x; i < kHlTile * p.tail; i += blockDim.x) {
+      const int r = i / p.tail, t = i % p.tail;
+      if (r0 + r < p.n) out[static_cast<int64_t>(r0 + r) * p.out_row + p.N + t] = in[static_cast<int64_t>(r0 + r) * p.in_row + p.K + t];
+    }
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  const int chunks = (p.K + kHlTile - 1) / kHlTile;
+  request(0, 0);
+  for (int kc = 0; kc < chunks; ++kc) {
+    const int buf = kc & 1;
+    if (kc + 1 < chunks) {
+      request(kc + 1, buf ^ 1);            // (the buffer of the chunk before: every warp left it before the barrier at the end of that chunk)
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kHlTile / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, &As[buf][(warp * 16 + (lane & 15)) * kHlLd + kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, &Bs[buf][(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kHlLd + nt * 16 + (lane >> 4) * 8]);
+        mma_bf16(acc[2 * nt], a, b[0], b[1]);
+        mma_bf16(acc[2 * nt + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = r0 + warp * 16 + (lane >> 2) + half * 8;
+    if (r >= p.n) continue;
+    bf16* dst = out + static_cast<int64_t>(r) * p.out_row + n0 + (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = (i >> 1) * 16 + (i & 1) * 8;
+      if (n0 + c + (lane & 3) * 2 < p.N) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[i][2 * half], acc[i][2 * half + 1]);
+    }
+  }
+}
+
 struct TileParams {
   const bf16* q;             // [n][H D]
   bf16* out;                 // [n][H Dv]
@@ -654,6 +728,12 @@ SB_EXPORT int sb_head_linear(const void* in, int64_t in_row, int64_t in_head, co
   const size_t smem = sizeof(float) * TR * K;
   if (smem > 160 * 1024) return sb::fail("sb_head_linear: rows of %d elements do not fit the row buffer", K);
   HeadLinearParams p{in, in_row, in_head, w, out, out_row, out_head, n, H, K, N, tail};
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (dtype == 1 && aligned && K % 16 == 0 && N % 8 == 0 && in_row % 8 == 0 && in_head % 8 == 0 && out_row % 8 == 0 && out_head % 8 == 0) {
+    // (what decides for the tensor cores is the shape alone, never the number of rows: a token has one form whatever step it is in)
+    sb::launch_pdl(head_linear_tc_kernel, dim3((n + kHlTile - 1) / kHlTile, H, (N + kHlTile - 1) / kHlTile), dim3(128), 0, stream, p);
+    return sb::check_launch("sb_head_linear");
+  }
   const dim3 grid((n + TR - 1) / TR, H);
   if (dtype == 0) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(head_linear_kernel<float, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
