@@ -433,6 +433,7 @@ struct TileParams {
   int H, G, D, Dv, Dc;
   int window, keep_first;
   float scale;
+  int stages;                // 2: the next tile of keys is fetched while this one is worked on; 1: after it (half the shared memory)
 };
 
 constexpr int KT = 64, NK = KT / 16;
@@ -503,11 +504,20 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
     bf16* Vs = Ks + KT * ldk;
     for (int r = threadIdx.x >> shift; r < KT; r += blockDim.x >> shift) {
       const bf16* src = rowptr[buf * KT + r];
-      for (int c = threadIdx.x & (per_row - 1); c < cpr; c += per_row) {
-        const bool is_v = c >= dchunks;
-        bf16* dst = is_v ? Vs + r * ldv + (c - dchunks) * 8 : Ks + r * ldk + c * 8;
-        if (src != nullptr) copy16(dst, src + (is_v ? p.v_offset + (c - dchunks) * 8 : c * 8));
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      const int c0 = threadIdx.x & (per_row - 1);
+      bf16* kd = Ks + r * ldk;
+      bf16* vd = Vs + r * ldv;
+      if (src != nullptr && !own_values) {
+#pragma unroll 4
+        for (int c = c0; c < dchunks; c += per_row) copy16(kd + c * 8, src + c * 8);
+      } else if (src != nullptr) {             // the key's and the value's chunks side by side over the row's threads
+        const bf16* vsrc = src + p.v_offset - dchunks * 8;
+        for (int c = c0; c < cpr; c += per_row) {
+          if (c < dchunks) copy16(kd + c * 8, src + c * 8);
+          else copy16(vd + (c - dchunks) * 8, vsrc + c * 8);
+        }
+      } else {
+        for (int c = c0; c < cpr; c += per_row) *reinterpret_cast<uint4*>(c < dchunks ? kd + c * 8 : vd + (c - dchunks) * 8) = make_uint4(0, 0, 0, 0);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -519,9 +529,10 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
   };
   int kt = kt_keep >= 0 ? 0 : kt_first, buf = 0;
   request(kt, 0);
-  for (; kt <= kt_last; buf ^= 1) {
+  const bool two = p.stages == 2;
+  for (; kt <= kt_last; buf = two ? buf ^ 1 : 0) {
     const int kt_next = next_tile(kt);
-    if (kt_next <= kt_last) {
+    if (two && kt_next <= kt_last) {
       request(kt_next, buf ^ 1);           // (the buffer of the tile before: every warp left it before the barrier at the end of that tile)
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
@@ -531,16 +542,40 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
     const bf16* Ks = stage0 + buf * stage_elems;
     const bf16* Vs = own_values ? Ks + KT * ldk : Ks;
     // the scores of this warp's 16 keys
+    // (with long value rows, where registers are there for it: four sums side by side, each over every fourth step of 16 elements, so that a
+    // product does not wait for the one before it; they are joined in a fixed order: a row's score depends on the row and the key alone)
+    constexpr int CH = NVW >= 4 ? 4 : 1;
+    float s4[CH][2][4];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) s4[c][i][0] = s4[c][i][1] = s4[c][i][2] = s4[c][i][3] = 0.0f;
+    const bf16* q_at = Qs + (lane & 15) * ldk + (lane >> 4) * 8;
+    const bf16* k_at = Ks + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + ((lane >> 3) & 1) * 8;
+    int k0 = 0;
+    if (CH > 1)
+      for (; k0 + 16 * CH <= p.D; k0 += 16 * CH) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          uint32_t a[4], b[4];
+          ldmatrix_x4(a, q_at + k0 + 16 * c);
+          ldmatrix_x4(b, k_at + k0 + 16 * c);
+          mma_bf16(s4[c][0], a, b[0], b[1]);
+          mma_bf16(s4[c][1], a, b[2], b[3]);
+        }
+      }
+    for (; k0 < p.D; k0 += 16) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, q_at + k0);
+      ldmatrix_x4(b, k_at + k0);
+      mma_bf16(s4[0][0], a, b[0], b[1]);
+      mma_bf16(s4[0][1], a, b[2], b[3]);
+    }
     float s[2][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-    for (int k0 = 0; k0 < p.D; k0 += 16) {
-      uint32_t a[4], b[4];
-      ldmatrix_x4(a, Qs + (lane & 15) * ldk + k0 + (lane >> 4) * 8);
-      ldmatrix_x4(b, Ks + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + k0 + ((lane >> 3) & 1) * 8);
-      mma_bf16(s[0], a, b[0], b[1]);
-      mma_bf16(s[1], a, b[2], b[3]);
-    }
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i][e] = CH == 4 ? (s4[0][i][e] + s4[CH > 1 ? 1 : 0][i][e]) + (s4[CH > 2 ? 2 : 0][i][e] + s4[CH > 3 ? 3 : 0][i][e]) : s4[0][i][e];
     float top_lo = -INFINITY, top_hi = -INFINITY;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -593,20 +628,28 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
         hi[i] = Ps[((0 * NK + kk) * 4 + i) * 32 + lane];
         lo[i] = Ps[((1 * NK + kk) * 4 + i) * 32 + lane];
       }
+      // the step's value fragments first, then the products of the first parts for every column group, then those of the second parts:
+      // a column's sum takes its terms in the same order (hi, then lo), with the other columns' products between the two
+      uint32_t b[NVW][4];
+      const bf16* v_at = Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + (lane >> 4) * 8;
 #pragma unroll
-      for (int i = 0; i < NVW; ++i) {
-        const int nv = warp + 4 * i;
-        if (nv < NV) {
-          uint32_t b[4];
-          ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + nv * 16 + (lane >> 4) * 8);
-          mma_bf16(o[2 * i], hi, b[0], b[1]);
-          mma_bf16(o[2 * i], lo, b[0], b[1]);
-          mma_bf16(o[2 * i + 1], hi, b[2], b[3]);
-          mma_bf16(o[2 * i + 1], lo, b[2], b[3]);
+      for (int i = 0; i < NVW; ++i)
+        if (warp + 4 * i < NV) ldmatrix_x4_trans(b[i], v_at + (warp + 4 * i) * 16);
+#pragma unroll
+      for (int i = 0; i < NVW; ++i)
+        if (warp + 4 * i < NV) {
+          mma_bf16(o[2 * i], hi, b[i][0], b[i][1]);
+          mma_bf16(o[2 * i + 1], hi, b[i][2], b[i][3]);
         }
-      }
+#pragma unroll
+      for (int i = 0; i < NVW; ++i)
+        if (warp + 4 * i < NV) {
+          mma_bf16(o[2 * i], lo, b[i][0], b[i][1]);
+          mma_bf16(o[2 * i + 1], lo, b[i][2], b[i][3]);
+        }
     }
     __syncthreads();                      // the tile's buffer, the maxima and the exchanged operands may be written again
+    if (!two && kt_next <= kt_last) request(kt_next, 0);
     kt = kt_next;
   }
   // the rows' sums: a thread's share over its columns, the four lanes of a row, then the warps in ascending order; then the sink
@@ -639,15 +682,27 @@ template <int NVW>
 int launch_tiles(const TileParams& p, int n, cudaStream_t stream) {
   const int Hg = p.H / p.G, Ht = Hg < 16 ? Hg : 16, PT = 16 / Ht;
   const bool own_values = p.v_offset != 0;
-  const size_t smem = 2 * KT * sizeof(void*) + 2 * NK * 4 * 32 * sizeof(uint32_t) + 4 * 16 * sizeof(float) +
-                      sizeof(bf16) * (16 * (p.D + 8) + 2 * KT * (p.D + 8 + (own_values ? p.Dv + 8 : 0)));
+  const size_t fixed = 2 * KT * sizeof(void*) + 2 * NK * 4 * 32 * sizeof(uint32_t) + 4 * 16 * sizeof(float) + sizeof(bf16) * 16 * (p.D + 8);
+  const size_t stage = sizeof(bf16) * KT * (p.D + 8 + (own_values ? p.Dv + 8 : 0));
+  size_t smem = fixed + 2 * stage;
   if (smem > 220 * 1024) return sb::fail("sb_masked_attention_tiles: key size %d and value size %d need %zu bytes of shared memory", p.D, p.Dv, smem);
+  const dim3 grid((n + PT - 1) / PT + p.entries, p.G * (Hg / Ht));
+  TileParams q = p;
+  q.stages = 2;
+  // rows so long that two stages leave room for one CTA on an SM: with CTAs enough for two on every SM, one stage each and two CTAs that
+  // fill each other's waits do better. The arithmetic is the same either way.
+  constexpr size_t kHalfSm = 113 * 1024;
+  if (smem > kHalfSm && fixed + stage <= kHalfSm && static_cast<int64_t>(grid.x) * grid.y >= 2 * sb::sm_count()) {
+    q.stages = 1;
+    smem = fixed + stage;
+  }
   static sb::DeviceOnce once;
   if (once.needed()) {
     cudaFuncSetAttribute(masked_attention_tile_kernel<NVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     once.done();
   }
-  sb::launch_pdl(masked_attention_tile_kernel<NVW>, dim3((n + PT - 1) / PT + p.entries, p.G * (Hg / Ht)), dim3(128), smem, stream, p);
+  sb::prefer_max_shared(reinterpret_cast<const void*>(masked_attention_tile_kernel<NVW>));
+  sb::launch_pdl(masked_attention_tile_kernel<NVW>, grid, dim3(128), smem, stream, q);
   return sb::check_launch("sb_masked_attention_tiles");
 }
 
@@ -789,7 +844,7 @@ SB_EXPORT int sb_masked_attention_tiles(const void* q, void* out, const void* pa
     return sb::fail("sb_masked_attention_tiles: heads %d / %d, key size %d, value size %d are not a shape of the tensor-core form", H, G, D, Dv);
   if (window < 0 || keep_first < 0) return sb::fail("sb_masked_attention_tiles: window %d, kept first tokens %d", window, keep_first);
   TileParams p{static_cast<const bf16*>(q), static_cast<bf16*>(out), static_cast<const bf16*>(pages), block_table, max_pages, page_size, page_stride,
-               v_offset, head_stride, meta, meta_stride, entries, slopes, sinks, H, G, D, Dv, Dc, window, keep_first, scale};
+               v_offset, head_stride, meta, meta_stride, entries, slopes, sinks, H, G, D, Dv, Dc, window, keep_first, scale, 2};
   const int groups = (Dv / 16 + 3) / 4;
   switch (groups) {
     case 1: return launch_tiles<1>(p, n, stream);
