@@ -136,34 +136,30 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
   }
 }
 
-// A block per row; the row's expert weights in shared memory first. GATED: an expert has 2 F rows of `up`, F gate rows and then F up
-// rows, and its hidden activation is silu(gate) * up instead of relu(up)^2.
+// A block per row and expert; an expert that the row did not choose (weight 0) is zeroed without reading. GATED: an expert has 2 F rows
+// of `up`, F gate rows and then F up rows, and its hidden activation is silu(gate) * up instead of relu(up)^2.
 template <class TO, bool GATED>
 __global__ void __launch_bounds__(256) moe_activate_kernel(const float* __restrict__ up, int n_partials, int64_t partial_stride,
                                                            const float* __restrict__ weights, int ldw, TO* __restrict__ out, int E, int F) {
-  __shared__ float g[256];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int64_t r = blockIdx.x;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) g[e] = weights[r * ldw + e];
-  __syncthreads();
+  const int e = blockIdx.y;                      // a CTA per (row, expert): a step of few rows still fills the SMs
   const int EF = E * F;
   const float* src = up + r * EF * (GATED ? 2 : 1);
   TO* dst = out + r * EF;
-  for (int e = 0; e < E; ++e) {
-    const float w = g[e];
-    if (w == 0.0f) {
-      for (int j = threadIdx.x; j < F; j += blockDim.x) dst[e * F + j] = sb::narrow<TO>(0.0f);
+  const float w = weights[r * ldw + e];
+  if (w == 0.0f) {
+    for (int j = threadIdx.x; j < F; j += blockDim.x) dst[e * F + j] = sb::narrow<TO>(0.0f);
+    return;
+  }
+  for (int j = threadIdx.x; j < F; j += blockDim.x) {
+    if (GATED) {
+      const float g = folded(src + 2 * e * F + j, n_partials, partial_stride), u = folded(src + (2 * e + 1) * F + j, n_partials, partial_stride);
+      dst[e * F + j] = sb::narrow<TO>(w * ((g / (1.0f + expf(-g))) * u));
     } else {
-      for (int j = threadIdx.x; j < F; j += blockDim.x) {
-        if (GATED) {
-          const float g = folded(src + 2 * e * F + j, n_partials, partial_stride), u = folded(src + (2 * e + 1) * F + j, n_partials, partial_stride);
-          dst[e * F + j] = sb::narrow<TO>(w * ((g / (1.0f + expf(-g))) * u));
-        } else {
-          const float z = fmaxf(folded(src + e * F + j, n_partials, partial_stride), 0.0f);
-          dst[e * F + j] = sb::narrow<TO>(w * (z * z));
-        }
-      }
+      const float z = fmaxf(folded(src + e * F + j, n_partials, partial_stride), 0.0f);
+      dst[e * F + j] = sb::narrow<TO>(w * (z * z));
     }
   }
 }
@@ -216,7 +212,7 @@ SB_EXPORT int sb_moe_activate(const float* up, int n_partials, int64_t partial_s
   if (n <= 0) return 0;
   if (n_partials < 1 || E <= 0 || F <= 0) return sb::fail("sb_moe_activate: n_partials %d, %d experts of %d", n_partials, E, F);
   if (E > 256) return sb::fail("sb_moe_activate: %d experts (at most 256)", E);
-#define SB_ACT(TO, G) sb::launch_pdl(moe_activate_kernel<TO, G>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<TO*>(out), E, F)
+#define SB_ACT(TO, G) sb::launch_pdl(moe_activate_kernel<TO, G>, dim3(n, E), dim3(F >= 1024 ? 256 : 128), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<TO*>(out), E, F)
   if (out_dtype == 0) {
     if (gated) SB_ACT(float, true);
     else SB_ACT(float, false);

@@ -201,7 +201,7 @@ def test_a_key_at_a_window_or_kept_edge_decides_the_row(distance, seen, tiles):
 
 
 @pytest.mark.parametrize("H,G,D,V,window,keep,page", [(8, 2, 64, 64, 100, 33, 32), (4, 2, 32, 48, 24, 5, 16), (2, 2, 96, 96, 72, 0, 64),
-                                                      (16, 1, 16, 128, 0, 0, 8), (8, 4, 64, 48, 96, 20, 16), (4, 4, 256, 16, 200, 1, 16)])
+                                                      (16, 1, 16, 128, 0, 0, 8), (8, 4, 32, 80, 90, 21, 16), (4, 4, 256, 16, 200, 1, 16)])
 def test_masked_attention_on_the_tensor_cores(H, G, D, V, window, keep, page):
     """The bfloat16 tile kernel against the plain attention that rounds q, k and v to bfloat16 (its weights stay 32-bit), and against
     the kernel with a block per token and head on the same inputs; with queries scaled down, so that every visible key weighs alike
@@ -219,7 +219,7 @@ def test_masked_attention_on_the_tensor_cores(H, G, D, V, window, keep, page):
 
 @pytest.mark.parametrize("H,D,R,V,Q,C,page,scaling", [(3, 20, 12, 28, 36, 44, 16, (8.0, 64, 16.0, 2.0)), (8, 32, 32, 32, 64, 96, 32, (2.0, 128, 8.0, 1.0)),
                                                       (2, 16, 16, 64, 32, 48, 8, None), (1, 8, 4, 8, 8, 16, 8, (4.0, 32, 4.0, 0.5)),
-                                                      (4, 64, 16, 48, 80, 112, 16, (4.0, 256, 32.0, 1.0))])
+                                                      (4, 48, 16, 40, 72, 112, 16, (3.0, 256, 24.0, 1.5))])
 def test_latent_attention_kernels(H, D, R, V, Q, C, page, scaling):
     """The latents normed and the shared rotated key part appended as one row per token, the queries' rotated slices, the key
     projection taken into the queries, attention over the latent rows, the value projection behind it: against the plain latent
