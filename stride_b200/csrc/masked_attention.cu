@@ -554,14 +554,17 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
     const bf16* k_at = Ks + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + ((lane >> 3) & 1) * 8;
     int k0 = 0;
     if (CH > 1)
-      for (; k0 + 16 * CH <= p.D; k0 += 16 * CH) {
+      for (; k0 + 16 * CH <= p.D; k0 += 16 * CH) {       // the four steps' fragments first, then their products
+        uint32_t a[CH][4], b[CH][4];
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
-          uint32_t a[4], b[4];
-          ldmatrix_x4(a, q_at + k0 + 16 * c);
-          ldmatrix_x4(b, k_at + k0 + 16 * c);
-          mma_bf16(s4[c][0], a, b[0], b[1]);
-          mma_bf16(s4[c][1], a, b[2], b[3]);
+          ldmatrix_x4(a[c], q_at + k0 + 16 * c);
+          ldmatrix_x4(b[c], k_at + k0 + 16 * c);
+        }
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          mma_bf16(s4[c][0], a[c], b[c][0], b[c][1]);
+          mma_bf16(s4[c][1], a[c], b[c][2], b[c][3]);
         }
       }
     for (; k0 < p.D; k0 += 16) {
