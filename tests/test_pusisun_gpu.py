@@ -201,7 +201,8 @@ def test_a_key_at_a_window_or_kept_edge_decides_the_row(distance, seen, tiles):
 
 
 @pytest.mark.parametrize("H,G,D,V,window,keep,page", [(8, 2, 64, 64, 100, 33, 32), (4, 2, 32, 48, 24, 5, 16), (2, 2, 96, 96, 72, 0, 64),
-                                                      (16, 1, 16, 128, 0, 0, 8), (8, 4, 32, 80, 90, 21, 16), (4, 4, 256, 16, 200, 1, 16)])
+                                                      (16, 1, 16, 128, 0, 0, 8), (8, 4, 32, 80, 90, 21, 16), (4, 4, 256, 16, 200, 1, 16),
+                                                      (32, 1, 16, 32, 50, 3, 16), (64, 2, 32, 16, 0, 0, 32)])
 def test_masked_attention_on_the_tensor_cores(H, G, D, V, window, keep, page):
     """The bfloat16 tile kernel against the plain attention that rounds q, k and v to bfloat16 (its weights stay 32-bit), and against
     the kernel with a block per token and head on the same inputs; with queries scaled down, so that every visible key weighs alike
