@@ -8,7 +8,7 @@ arhaamatiq/stride has no such registry: its loader never looks at `architectures
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable
+from typing import Callable, Optional
 
 from .llama import ConfigError
 
@@ -18,6 +18,7 @@ class Architecture:
     name: str
     parse_config: Callable      # dict (config.json) -> typed configuration
     model_spec: Callable        # typed configuration -> ModelSpec
+    complete_config: Optional[Callable] = None   # (config.json dict, {tensor name: shape}) -> dict: sizes that only the checkpoint's shapes tell
 
 
 _ARCHITECTURES: dict = {}

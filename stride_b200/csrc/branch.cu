@@ -305,3 +305,69 @@ SB_EXPORT int sb_op_row_scaled_add(const SbOp* op, const SbStep* s, void* stream
   return sb_row_scaled_add(ptr<float>(op->i[0]), ptr<const void>(op->i[1]), (int)op->i[2], ptr<const float>(op->i[3]), (int)op->i[4], (int)op->i[5],
                            (int)op->i[6], s->n, (int)op->i[7], static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Two branches that are each RMS-normed over their row, with a gain of their own, before their weighted sum joins `dst`:
+//
+//   dst[r, j] += ca * ga[j] * A[r, j] / sqrt(mean_j(A[r, :]^2) + eps) + cb * gb[j] * B[r, j] / sqrt(mean_j(B[r, :]^2) + eps)
+//
+// with A = a + (pa_0 + pa_1 + ..), B likewise; the branch buffers are zero afterwards. What mixers side by side need whose results are
+// normed one by one. A block per row, both rows held in shared memory between the sums of squares and the add.
+namespace {
+
+template <class TG>
+__global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ ga,
+                                                                    const TG* __restrict__ gb, int W, float eps) {
+  extern __shared__ __align__(16) float row_values[];      // [2][W]
+  __shared__ float red[32];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
+  float sa = 0.0f, sb2 = 0.0f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float va = source_value<float>(a, row + c), vb = source_value<float>(b, row + c);
+    row_values[c] = va, row_values[W + c] = vb;
+    sa = fmaf(va, va, sa), sb2 = fmaf(vb, vb, sb2);
+  }
+  const float ra = mul(a.c, 1.0f / sqrtf(sb::block_sum(sa, red) / static_cast<float>(W) + eps));
+  const float rb = mul(b.c, 1.0f / sqrtf(sb::block_sum(sb2, red) / static_cast<float>(W) + eps));
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float va = mul(mul(row_values[c], ra), sb::widen(ga[c])), vb = mul(mul(row_values[W + c], rb), sb::widen(gb[c]));
+    dst[row + c] = add(dst[row + c], add(va, vb));
+  }
+}
+
+}  // namespace
+
+// i: 0 dst, 1 a, 2 a's partial sums (flat), 3 their K ranges S, 4 most tokens with a buffer per range, 5 b, 6 b's partial sums, 7 their S,
+//    8 a's gain, 9 b's gain, 10 the gains' dtype, 11 W
+// f: 0 ca, 1 cb, 2 eps
+SB_EXPORT int sb_op_branch_pair_norm_fold(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int W = (int)op->i[11];
+  const int64_t stride = static_cast<int64_t>(s->n) * W;
+  float* a = ptr<float>(op->i[1]);
+  float* b = ptr<float>(op->i[5]);
+  const float* pa = ptr<const float>(op->i[2]);
+  const float* pb = ptr<const float>(op->i[6]);
+  if ((a == nullptr && pa == nullptr) || (b == nullptr && pb == nullptr)) return sb::fail("sb_op_branch_pair_norm_fold: a branch with neither a buffer nor partial sums"), SB_OP_FAILED;
+  const Source A{a, pa, pa ? partial_count(op->i[3], op->i[4], s->n) : 0, stride, static_cast<float>(op->f[0])};
+  const Source B{b, pb, pb ? partial_count(op->i[7], op->i[4], s->n) : 0, stride, static_cast<float>(op->f[1])};
+  const size_t smem = static_cast<size_t>(2) * W * sizeof(float);
+  if (smem > 160 * 1024) return sb::fail("sb_op_branch_pair_norm_fold: rows of %d elements do not fit the row buffer", W), SB_OP_FAILED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int threads = W >= 1024 ? 256 : 128;
+  if (op->i[10] == 0) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(branch_pair_norm_fold_kernel<float>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const float>(op->i[8]),
+                   ptr<const float>(op->i[9]), W, static_cast<float>(op->f[2]));
+  } else if (op->i[10] == 1) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(branch_pair_norm_fold_kernel<bf16>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const bf16>(op->i[8]),
+                   ptr<const bf16>(op->i[9]), W, static_cast<float>(op->f[2]));
+  } else {
+    return sb::fail("sb_op_branch_pair_norm_fold: unsupported gain dtype %d", (int)op->i[10]), SB_OP_FAILED;
+  }
+  return sb::check_launch("sb_op_branch_pair_norm_fold");
+}

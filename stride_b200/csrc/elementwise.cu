@@ -427,3 +427,121 @@ SB_EXPORT int sb_op_concat_rows(const SbOp* op, const SbStep* s, void* stream) {
   return sb_concat_rows(ptr<float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[7], ptr<const float>(op->i[4]),
                         ptr<void>(op->i[5]), (int)op->i[6], s->n, (int)op->i[7], (int)op->i[8], static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// A per-layer input that depends on the token alone (a second, narrow embedding table with a slice per layer):
+// `stream_cast_kernel` folds the pending partial sums into the residual stream and leaves a copy of the rows in the activations' dtype,
+// the input of a projection that reads the stream itself, not a normed copy; `token_gate_kernel` makes
+// out[r, j] = act(gate[r, j]) * table[token_r, offset + j], the gate being a projection's partial sums, act the tanh form of gelu or silu.
+namespace {
+
+template <class TO>
+__global__ void __launch_bounds__(256) stream_cast_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials, int64_t stride,
+                                                          TO* __restrict__ out, int W) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = h[row + c];
+    if (partials != nullptr) {
+      float sum = partials[row + c];
+      for (int s = 1; s < n_partials; ++s) sum += partials[s * stride + row + c];
+      v += sum;
+      h[row + c] = v;
+    }
+    out[row + c] = sb::narrow<TO>(v);
+  }
+}
+
+template <class TT, class TO>
+__global__ void __launch_bounds__(128) token_gate_kernel(const float* __restrict__ gate, int n_partials, int64_t stride, int width,
+                                                         const int32_t* __restrict__ tokens, const int32_t* __restrict__ slots,
+                                                         const int32_t* __restrict__ sampled, const TT* __restrict__ table, int table_width,
+                                                         int offset, int vocab, TO* __restrict__ out, int gelu) {
+  sb::grid_launch_dependents();
+  const int row = blockIdx.x;
+  sb::grid_dependency_wait();
+  int tok = tokens[row];
+  if (tok == -1 && sampled != nullptr) tok = sampled[slots[row]];
+  const bool ok = tok >= 0 && tok < vocab;
+  const TT* e = table + static_cast<int64_t>(ok ? tok : 0) * table_width + offset;
+  const float* g = gate + static_cast<int64_t>(row) * width;
+  for (int j = threadIdx.x; j < width; j += blockDim.x) {
+    float z = g[j];
+    for (int s = 1; s < n_partials; ++s) z += g[s * stride + j];
+    float a;
+    if (gelu) a = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else a = z / (1.0f + expf(-z));
+    out[static_cast<int64_t>(row) * width + j] = sb::narrow<TO>(ok ? __fmul_rn(a, sb::widen(e[j])) : 0.0f);
+  }
+}
+
+}  // namespace
+
+// i: 0 h (float32 [n, W]), 1 pending partial sums (flat; 0: none), 2 K ranges S, 3 most tokens with a buffer per range, 4 out, 5 out dtype, 6 W
+SB_EXPORT int sb_op_stream_cast(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int W = (int)op->i[6];
+  const float* partials = ptr<const float>(op->i[1]);
+  const int P = partials ? partial_count(op->i[2], op->i[3], s->n) : 0;
+  const int64_t stride = static_cast<int64_t>(s->n) * W;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (op->i[5] == 0) sb::launch_pdl(stream_cast_kernel<float>, dim3(s->n), dim3(256), 0, st, ptr<float>(op->i[0]), partials, P, stride, ptr<float>(op->i[4]), W);
+  else if (op->i[5] == 1) sb::launch_pdl(stream_cast_kernel<bf16>, dim3(s->n), dim3(256), 0, st, ptr<float>(op->i[0]), partials, P, stride, ptr<bf16>(op->i[4]), W);
+  else return sb::fail("sb_op_stream_cast: unsupported dtype %d", (int)op->i[5]), SB_OP_FAILED;
+  return sb::check_launch("sb_op_stream_cast");
+}
+
+// i: 0 the gate's partial sums (flat), 1 their width (= the slice's width), 2 K ranges S, 3 most tokens with a buffer per range, 4 table,
+//    5 table dtype, 6 the table's row width, 7 the slice's first column, 8 vocab, 9 the table of last sampled tokens (or 0), 10 out, 11 out dtype,
+//    12 the gate's activation (0 silu, 1 tanh form of gelu)
+SB_EXPORT int sb_op_token_gate(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[1];
+  const int P = partial_count(op->i[2], op->i[3], s->n);
+  const int64_t stride = static_cast<int64_t>(s->n) * width;
+  const int32_t* sampled = ptr<const int32_t>(op->i[9]);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define SB_TG(TT, TO)                                                                                                                         \
+  sb::launch_pdl(token_gate_kernel<TT, TO>, dim3(s->n), dim3(128), 0, st, ptr<const float>(op->i[0]), P, stride, width, tokens(s), slots(s), \
+                 sampled, ptr<const TT>(op->i[4]), (int)op->i[6], (int)op->i[7], (int)op->i[8], ptr<TO>(op->i[10]), (int)op->i[12])
+  if (op->i[5] == 0 && op->i[11] == 0) SB_TG(float, float);
+  else if (op->i[5] == 1 && op->i[11] == 0) SB_TG(bf16, float);
+  else if (op->i[5] == 0 && op->i[11] == 1) SB_TG(float, bf16);
+  else if (op->i[5] == 1 && op->i[11] == 1) SB_TG(bf16, bf16);
+  else return sb::fail("sb_op_token_gate: unsupported dtypes %d, %d", (int)op->i[5], (int)op->i[11]), SB_OP_FAILED;
+#undef SB_TG
+  return sb::check_launch("sb_op_token_gate");
+}
+
+namespace {
+template <class TO>
+__global__ void __launch_bounds__(256) cast_columns_kernel(const float* __restrict__ src, int n_partials, int64_t stride, int width, int first, int count,
+                                                           TO* __restrict__ out) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const float* row = src + static_cast<int64_t>(blockIdx.x) * width + first;
+  for (int j = threadIdx.x; j < count; j += blockDim.x) {
+    float v = row[j];
+    for (int s = 1; s < n_partials; ++s) v += row[s * stride + j];
+    out[static_cast<int64_t>(blockIdx.x) * count + j] = sb::narrow<TO>(v);
+  }
+}
+}  // namespace
+
+// A column range of a projection's partial sums, folded, as a matrix of its own in the activations' dtype (the input of a second projection).
+// i: 0 partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 first column, 5 columns, 6 out, 7 out dtype
+SB_EXPORT int sb_op_cast_columns(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[1];
+  const int P = partial_count(op->i[2], op->i[3], s->n);
+  const int64_t stride = static_cast<int64_t>(s->n) * width;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (op->i[7] == 0) sb::launch_pdl(cast_columns_kernel<float>, dim3(s->n), dim3(256), 0, st, ptr<const float>(op->i[0]), P, stride, width, (int)op->i[4], (int)op->i[5], ptr<float>(op->i[6]));
+  else if (op->i[7] == 1) sb::launch_pdl(cast_columns_kernel<bf16>, dim3(s->n), dim3(256), 0, st, ptr<const float>(op->i[0]), P, stride, width, (int)op->i[4], (int)op->i[5], ptr<bf16>(op->i[6]));
+  else return sb::fail("sb_op_cast_columns: unsupported dtype %d", (int)op->i[7]), SB_OP_FAILED;
+  return sb::check_launch("sb_op_cast_columns");
+}

@@ -293,9 +293,13 @@ __global__ void __launch_bounds__(512, 2) lightning_step_kernel(const ScanParams
     if (j < 2 * Dp) {
       const bool is_k = j >= Dp;
       const int d = is_k ? j - Dp : j;
-      if (d < p.D) v = silu(folded(src + (is_k ? p.k_off : p.q_off) + h * p.D + d, p.n_partials, p.partial_stride));
+      if (d < p.D) {
+        v = folded(src + (is_k ? p.k_off : p.q_off) + h * p.D + d, p.n_partials, p.partial_stride);
+        if (!p.activated) v = silu(v);
+      }
     } else if (c0 + j - 2 * Dp < p.V) {
-      v = silu(folded(src + p.v_off + h * p.V + c0 + j - 2 * Dp, p.n_partials, p.partial_stride));
+      v = folded(src + p.v_off + h * p.V + c0 + j - 2 * Dp, p.n_partials, p.partial_stride);
+      if (!p.activated) v = silu(v);
     }
     smem[j] = v;
   }
@@ -361,9 +365,11 @@ __global__ void __launch_bounds__(1024) gated_rmsnorm_kernel(const float* __rest
 // on the device; state [slots][H][D][V] float32; out [n][H V] float32.
 // act: scratch [n][q, k, v columns] float32. Steps in which an entry brings several tokens apply the activation in a kernel
 // of its own first; steps of single tokens apply it inside theirs (the same function on the same sums: the same bits).
-SB_EXPORT int sb_lightning_scan(const float* proj, int n_partials, int64_t partial_stride, int width, int q_off, int k_off, int v_off,
-                                const int32_t* meta, int meta_stride, int entries, int n, const float* decay, float* state, float* out,
-                                float* act, int H, int D, int V, cudaStream_t stream) {
+// `ready` = 1: `proj` already holds q, k and v as the recurrence takes them (another design's activation, made by a kernel in front), and
+// nothing is applied here.
+SB_EXPORT int sb_lightning_scan_ex(const float* proj, int n_partials, int64_t partial_stride, int width, int q_off, int k_off, int v_off,
+                                   const int32_t* meta, int meta_stride, int entries, int n, const float* decay, float* state, float* out,
+                                   float* act, int H, int D, int V, int ready, cudaStream_t stream) {
   if (entries <= 0 || n <= 0) return 0;
   if (H <= 0 || D <= 0 || V <= 0 || D > 256) return sb::fail("sb_lightning_scan: heads %d, key size %d (at most 256), value size %d", H, D, V);
   if (n_partials < 1) return sb::fail("sb_lightning_scan: n_partials must be >= 1");
@@ -374,14 +380,17 @@ SB_EXPORT int sb_lightning_scan(const float* proj, int n_partials, int64_t parti
   const long long sms = sb::sm_count();
   while (vw > 1 && static_cast<long long>(entries) * H * ((v_warps + vw - 1) / vw) < 2 * sms) --vw;
   if (n == entries) {     // one token an entry (decoding): small CTAs, many of them, nothing staged ahead
-    ScanParams p{proj, n_partials, partial_stride, width, q_off, k_off, v_off, meta, meta_stride, decay, state, out, H, D, V, 32, 1, 0};
+    ScanParams p{proj, n_partials, partial_stride, width, q_off, k_off, v_off, meta, meta_stride, decay, state, out, H, D, V, 32, 1, ready};
     sb::launch_pdl(lightning_step_kernel, dim3(entries, H, v_warps), dim3(parts * 32), sizeof(float) * (2 * Dp + 32 + parts * 32), stream, p);
     return sb::check_launch("sb_lightning_scan");
   }
   // steps with longer entries: the activation once for all tokens, then the recurrence
-  if (act == nullptr) return sb::fail("sb_lightning_scan: a step with an entry of several tokens needs the scratch for the activated sums");
-  const int cols = max(max(q_off + H * D, k_off + H * D), v_off + H * V);
-  {
+  if (act == nullptr && !ready) return sb::fail("sb_lightning_scan: a step with an entry of several tokens needs the scratch for the activated sums");
+  const int cols = ready ? width : max(max(q_off + H * D, k_off + H * D), v_off + H * V);
+  if (ready) {
+    if (n_partials != 1) return sb::fail("sb_lightning_scan: ready-made q, k, v come as one buffer");
+    act = const_cast<float*>(proj);
+  } else {
     const int64_t total = static_cast<int64_t>(n) * cols;
     const int blocks = static_cast<int>((total + 255) / 256 < sms * 16 ? (total + 255) / 256 : sms * 16);
     sb::launch_pdl(lightning_activate_kernel, dim3(blocks), dim3(256), 0, stream, proj, n_partials, partial_stride, width, act, n, cols);
@@ -401,6 +410,13 @@ SB_EXPORT int sb_lightning_scan(const float* proj, int n_partials, int64_t parti
     sb::launch_pdl(lightning_scan_kernel<1>, grid, dim3(threads), smem, stream, p);
   }
   return sb::check_launch("sb_lightning_scan");
+}
+
+SB_EXPORT int sb_lightning_scan(const float* proj, int n_partials, int64_t partial_stride, int width, int q_off, int k_off, int v_off,
+                                const int32_t* meta, int meta_stride, int entries, int n, const float* decay, float* state, float* out,
+                                float* act, int H, int D, int V, cudaStream_t stream) {
+  return sb_lightning_scan_ex(proj, n_partials, partial_stride, width, q_off, k_off, v_off, meta, meta_stride, entries, n, decay, state, out, act,
+                              H, D, V, 0, stream);
 }
 
 // out [n][W] (float32 or bfloat16) = rmsnorm(o [n][W] float32) * gain * sigmoid(gate), the gate being columns g_off.. of `proj`.
@@ -428,15 +444,16 @@ SB_EXPORT int sb_gated_rmsnorm(const float* o, const float* proj, int n_partials
 
 // ------------------------------------------------------------------ operations of the native step program (step_ops.h)
 // i: 0 projection partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 q_off, 5 k_off,
-//    6 v_off, 7 decay (float32 [H]), 8 state, 9 out (float32 [n, H V]), 10 H, 11 D, 12 V, 13 scratch for the activated sums
+//    6 v_off, 7 decay (float32 [H]), 8 state, 9 out (float32 [n, H V]), 10 H, 11 D, 12 V, 13 scratch for the activated sums,
+//    14 q, k, v are ready-made (one buffer, nothing applied)
 SB_EXPORT int sb_op_lightning_scan(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
   const int P = partial_count(op->i[2], op->i[3], s->n);
-  return sb_lightning_scan(ptr<const float>(op->i[0]), P, static_cast<int64_t>(s->n) * op->i[1], (int)op->i[1], (int)op->i[4], (int)op->i[5],
-                           (int)op->i[6], entry_meta(s), s->max_rows, s->entries, s->n, ptr<const float>(op->i[7]), ptr<float>(op->i[8]),
-                           ptr<float>(op->i[9]), ptr<float>(op->i[13]), (int)op->i[10], (int)op->i[11], (int)op->i[12],
-                           static_cast<cudaStream_t>(stream));
+  return sb_lightning_scan_ex(ptr<const float>(op->i[0]), P, static_cast<int64_t>(s->n) * op->i[1], (int)op->i[1], (int)op->i[4], (int)op->i[5],
+                              (int)op->i[6], entry_meta(s), s->max_rows, s->entries, s->n, ptr<const float>(op->i[7]), ptr<float>(op->i[8]),
+                              ptr<float>(op->i[9]), ptr<float>(op->i[13]), (int)op->i[10], (int)op->i[11], (int)op->i[12], (int)op->i[14],
+                              static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 o (float32 [n, W]), 1 projection partial sums (flat), 2 their width, 3 K ranges S, 4 most tokens with a buffer per range,
@@ -449,4 +466,130 @@ SB_EXPORT int sb_op_gated_rmsnorm(const SbOp* op, const SbStep* s, void* stream)
   return sb_gated_rmsnorm(ptr<const float>(op->i[0]), ptr<const float>(op->i[1]), P, static_cast<int64_t>(s->n) * op->i[2], (int)op->i[2],
                           (int)op->i[5], ptr<const void>(op->i[6]), (int)op->i[7], ptr<void>(op->i[8]), (int)op->i[9], s->n, (int)op->i[10],
                           static_cast<float>(op->f[0]), static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Retention: the same recurrence with rotated, not activated, queries and keys, and what other linear-attention designs put behind it.
+//
+// `rotate_qk_kernel`: out[r] = [q | k | v] in 32-bit from the projection's partial sums: the first `rot` elements of every q and k head
+// turned by the token's position (pairs (i, i + rot / 2), or (2i, 2i + 1) when interleaved), k times a constant behind the rotation, v
+// as it is. The recurrence then takes the buffer as ready-made.
+//
+// `group_norm_gate_kernel`: every head's result divided by its root mean square, times a gain of the head's size shared by all heads
+// (or none), times silu or sigmoid of the gate, a column range of some projection's partial sums. A warp per (token, head).
+namespace {
+
+struct RotateParams {
+  const float* proj;
+  int n_partials;
+  int64_t partial_stride;
+  int width, q_off, k_off, v_off;
+  const int32_t* positions;
+  const float* cos_sin;      // [positions][rot / 2][2]
+  int rot, interleaved;
+  float k_scale;
+  float* out;                // [n][2 H D + H V]
+  int H, D, V;
+};
+
+__global__ void __launch_bounds__(256) rotate_qk_kernel(RotateParams p) {
+  sb::grid_launch_dependents();
+  const int row = blockIdx.x, nqk = 2 * p.H * p.D, cols = nqk + p.H * p.V, rh = p.rot / 2;
+  const int pos = p.positions[row];
+  sb::grid_dependency_wait();
+  const float* src = p.proj + static_cast<int64_t>(row) * p.width;
+  float* dst = p.out + static_cast<int64_t>(row) * cols;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < cols; i += gridDim.y * blockDim.x) {
+    if (i >= nqk) {
+      dst[i] = folded(src + p.v_off + (i - nqk), p.n_partials, p.partial_stride);
+      continue;
+    }
+    const bool is_k = i >= p.H * p.D;
+    const int e = is_k ? i - p.H * p.D : i, d = e % p.D;
+    const float* at = src + (is_k ? p.k_off : p.q_off) + e;
+    float v = folded(at, p.n_partials, p.partial_stride);
+    if (d < p.rot) {
+      int pair, other;
+      bool low;
+      if (p.interleaved) pair = d >> 1, low = (d & 1) == 0, other = low ? 1 : -1;
+      else low = d < rh, pair = low ? d : d - rh, other = low ? rh : -rh;
+      const float b = folded(at + other, p.n_partials, p.partial_stride);
+      const float2 cs = *reinterpret_cast<const float2*>(p.cos_sin + (static_cast<int64_t>(pos) * rh + pair) * 2);
+      v = low ? __fsub_rn(__fmul_rn(v, cs.x), __fmul_rn(b, cs.y)) : __fadd_rn(__fmul_rn(v, cs.x), __fmul_rn(b, cs.y));
+    }
+    dst[i] = is_k ? __fmul_rn(v, p.k_scale) : v;
+  }
+}
+
+struct GroupGateParams {
+  const float* o;            // [n][H V]
+  const float* proj;         // the gate's partial sums [P][n][width], columns g_off ..
+  int n_partials;
+  int64_t partial_stride;
+  int width, g_off;
+  const void* gain;          // [V] or null
+  int gain_bf16;
+  void* out;
+  int n, H, V, silu_gate;
+  float eps;
+};
+
+template <class TO>
+__global__ void __launch_bounds__(128) group_norm_gate_kernel(GroupGateParams p) {
+  sb::grid_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  sb::grid_dependency_wait();
+  if (unit >= static_cast<int64_t>(p.n) * p.H) return;
+  const int64_t row = unit / p.H;
+  const int h = static_cast<int>(unit % p.H);
+  const float* o = p.o + unit * p.V;
+  const float* gate = p.proj + row * p.width + p.g_off + h * p.V;
+  float ss = 0.0f;
+  for (int d = lane; d < p.V; d += 32) ss = fmaf(o[d], o[d], ss);
+  for (int k = 16; k > 0; k >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, k);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(p.V) + p.eps);
+  TO* out = static_cast<TO*>(p.out) + unit * p.V;
+  for (int d = lane; d < p.V; d += 32) {
+    float v = __fmul_rn(o[d], r);
+    if (p.gain != nullptr) v = __fmul_rn(v, p.gain_bf16 ? __bfloat162float(static_cast<const bf16*>(p.gain)[d]) : static_cast<const float*>(p.gain)[d]);
+    const float g = folded(gate + d, p.n_partials, p.partial_stride);
+    const float sg = 1.0f / (1.0f + expf(-g));
+    out[d] = sb::narrow<TO>(__fmul_rn(v, p.silu_gate ? g * sg : sg));
+  }
+}
+
+}  // namespace
+
+// i: 0 projection partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 q_off, 5 k_off, 6 v_off, 7 cos_sin,
+//    8 rot, 9 interleaved pairs, 10 out (float32 [n][2 H D + H V]), 11 H, 12 D, 13 V      f: 0 the constant on k
+SB_EXPORT int sb_op_rotate_qk(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[1], rot = (int)op->i[8], H = (int)op->i[11], D = (int)op->i[12], V = (int)op->i[13];
+  if (rot < 0 || rot % 2 != 0 || rot > D) return sb::fail("sb_op_rotate_qk: %d rotated elements of %d", rot, D), SB_OP_FAILED;
+  RotateParams p{ptr<const float>(op->i[0]), partial_count(op->i[2], op->i[3], s->n), static_cast<int64_t>(s->n) * width, width, (int)op->i[4],
+                 (int)op->i[5], (int)op->i[6], positions(s), ptr<const float>(op->i[7]), rot, (int)op->i[9], (float)op->f[0], ptr<float>(op->i[10]),
+                 H, D, V};
+  const int cols = 2 * H * D + H * V;
+  sb::launch_pdl(rotate_qk_kernel, dim3(s->n, (cols + 1023) / 1024), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+  return sb::check_launch("sb_op_rotate_qk");
+}
+
+// i: 0 o (float32 [n, H V]), 1 the gate's partial sums (flat), 2 their width, 3 K ranges S, 4 most tokens with a buffer per range, 5 g_off,
+//    6 gain ([V], or 0), 7 gain dtype, 8 out, 9 out dtype, 10 H, 11 V, 12 the gate's activation (0 sigmoid, 1 silu)      f: 0 eps
+SB_EXPORT int sb_op_group_norm_gate(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[2];
+  GroupGateParams p{ptr<const float>(op->i[0]), ptr<const float>(op->i[1]), partial_count(op->i[3], op->i[4], s->n), static_cast<int64_t>(s->n) * width,
+                    width, (int)op->i[5], ptr<const void>(op->i[6]), (int)(op->i[7] == 1), ptr<void>(op->i[8]), s->n, (int)op->i[10], (int)op->i[11],
+                    (int)op->i[12], (float)op->f[0]};
+  const int64_t units = static_cast<int64_t>(p.n) * p.H;
+  const dim3 grid(static_cast<unsigned>((units + 3) / 4));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (op->i[9] == 0) sb::launch_pdl(group_norm_gate_kernel<float>, grid, dim3(128), 0, st, p);
+  else if (op->i[9] == 1) sb::launch_pdl(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, st, p);
+  else return sb::fail("sb_op_group_norm_gate: unsupported dtype %d", (int)op->i[9]), SB_OP_FAILED;
+  return sb::check_launch("sb_op_group_norm_gate");
 }

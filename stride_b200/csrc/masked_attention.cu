@@ -1,7 +1,7 @@
 // Softmax attention over the paged cache with the masks and score terms that grouped-query and latent attention designs combine:
 //
 //   score(i, j) = scale * (q_i . k_j) - slope_h * (i - j)                 slope_h = 0: no distance term
-//   i sees j    if j <= i and (window = 0 or i - j < window or j < keep_first)
+//   i sees j    if j <= i and (window = 0 or i - j < window or j < keep_first) and (chunk = 0 or floor(i / chunk) = floor(j / chunk))
 //   o_i         = sum_j exp(score(i, j) - m) v_j / (sum_j exp(score(i, j) - m) + exp(sink_h - m))      without a sink: no second term
 //
 // Query head h reads key/value head h / (H / G). The key size D and the value size Dv may differ; a token's values lie `v_offset`
@@ -242,6 +242,8 @@ struct AttnParams {
   int H, G, D, Dv, Dc;
   int window, keep_first;
   float scale;
+  int chunk;                 // > 0: a row sees only the keys of its own chunk of this many positions, counted from position 0
+  int out_f32;               // 1: `out` is float32 whatever the storage of q and the cache
 };
 
 constexpr int kWarps = 4;
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(kWarps * 32) masked_attention_kernel(AttnParam
   const int row = blockIdx.x, h = blockIdx.y, g = h / (p.H / p.G);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[row], slot = p.slots[row];
-  const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int first = max(p.window > 0 ? max(0, pos - p.window + 1) : 0, p.chunk > 0 ? pos / p.chunk * p.chunk : 0);
   const int kept_end = p.window > 0 ? min(p.keep_first, first) : 0;      // keys 0 .. kept_end - 1 lie in front of the window and are seen
   const float slope = p.slopes != nullptr ? p.slopes[h] : 0.0f;
   const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
@@ -306,11 +308,12 @@ __global__ void __launch_bounds__(kWarps * 32) masked_attention_kernel(AttnParam
     factor[c] = expf(ml[c] - top);
     total = fmaf(ml[kWarps + c], factor[c], total);
   }
-  T* out = static_cast<T*>(p.out) + (static_cast<int64_t>(row) * p.H + h) * p.Dv;
+  const int64_t at = (static_cast<int64_t>(row) * p.H + h) * p.Dv;
   for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
     float o = 0.0f;
     for (int c = 0; c < kWarps; ++c) o = fmaf(sums[c * p.Dv + d], factor[c], o);
-    out[d] = sb::narrow<T>(o / total);
+    if (p.out_f32) static_cast<float*>(p.out)[at + d] = o / total;
+    else static_cast<T*>(p.out)[at + d] = sb::narrow<T>(o / total);
   }
 }
 
@@ -434,6 +437,8 @@ struct TileParams {
   int window, keep_first;
   float scale;
   int stages;                // 2: the next tile of keys is fetched while this one is worked on; 1: after it (half the shared memory)
+  int chunk;                 // > 0: a row sees only the keys of its own chunk of this many positions
+  int out_f32;               // 1: `out` is float32
 };
 
 constexpr int KT = 64, NK = KT / 16;
@@ -465,7 +470,7 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
   const int slot = p.meta[e], row0 = p.meta[p.meta_stride + e], pos0 = p.meta[3 * p.meta_stride + e];
   const int t0 = tile * PT, nt = min(PT, len - t0);            // positions pos0 + t0 .. + nt - 1
   const int first_pos = pos0 + t0, last_pos = first_pos + nt - 1;
-  const int first_key = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int first_key = max(p.window > 0 ? max(0, first_pos - p.window + 1) : 0, p.chunk > 0 ? first_pos / p.chunk * p.chunk : 0);
   const int kept = p.window > 0 ? p.keep_first : 0;
   const int kt_first = first_key / KT, kt_last = last_pos / KT;
   const int kt_keep = kept > 0 ? min((kept - 1) / KT, kt_last) : -1;          // the last tile with kept tokens
@@ -586,7 +591,7 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
       for (int c = 0; c < 4; ++c) {
         const int j = kt * KT + warp * 16 + n * 8 + (lane & 3) * 2 + (c & 1);
         const int pos = c < 2 ? p_lo : p_hi;
-        const bool seen = j <= pos && (p.window <= 0 || pos - j < p.window || j < p.keep_first);
+        const bool seen = j <= pos && (p.window <= 0 || pos - j < p.window || j < p.keep_first) && (p.chunk <= 0 || j >= pos / p.chunk * p.chunk);
         const float x = seen ? __fsub_rn(__fmul_rn(s[n][c], p.scale), __fmul_rn(c < 2 ? s_lo : s_hi, static_cast<float>(pos - j))) : -INFINITY;
         s[n][c] = x;
         if (c < 2) top_lo = fmaxf(top_lo, x);
@@ -669,11 +674,16 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
     const int r = half ? r_hi : r_lo;
     if (r / Ht >= nt) continue;
     const float inv = 1.0f / (half ? t_hi : t_lo);
-    bf16* dst = p.out + (static_cast<int64_t>(row0 + t0 + r / Ht) * p.H + head0 + r % Ht) * p.Dv + (lane & 3) * 2;
+    const int64_t at = (static_cast<int64_t>(row0 + t0 + r / Ht) * p.H + head0 + r % Ht) * p.Dv + (lane & 3) * 2;
+    bf16* dst = p.out + at;
+    float* dst32 = reinterpret_cast<float*>(p.out) + at;
 #pragma unroll
     for (int i = 0; i < NVW; ++i) {
       const int nv = warp + 4 * i;
-      if (nv < NV) {
+      if (nv < NV && p.out_f32) {
+        *reinterpret_cast<float2*>(dst32 + nv * 16) = make_float2(o[2 * i][2 * half] * inv, o[2 * i][2 * half + 1] * inv);
+        *reinterpret_cast<float2*>(dst32 + nv * 16 + 8) = make_float2(o[2 * i + 1][2 * half] * inv, o[2 * i + 1][2 * half + 1] * inv);
+      } else if (nv < NV) {
         *reinterpret_cast<__nv_bfloat162*>(dst + nv * 16) = __floats2bfloat162_rn(o[2 * i][2 * half] * inv, o[2 * i][2 * half + 1] * inv);
         *reinterpret_cast<__nv_bfloat162*>(dst + nv * 16 + 8) = __floats2bfloat162_rn(o[2 * i + 1][2 * half] * inv, o[2 * i + 1][2 * half + 1] * inv);
       }
@@ -805,16 +815,18 @@ SB_EXPORT int sb_head_linear(const void* in, int64_t in_row, int64_t in_head, co
   return sb::check_launch("sb_head_linear");
 }
 
-SB_EXPORT int sb_masked_attention(const void* q, void* out, int dtype, const void* pages, const int32_t* block_table, int max_pages, int page_size,
-                                  int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* positions, const int32_t* slots,
-                                  const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc, int window, int keep_first,
-                                  float scale, cudaStream_t stream) {
+// `chunk` > 0: a row sees only the keys of its own chunk of that many positions; `out_f32`: the result is stored as float32.
+SB_EXPORT int sb_masked_attention_ex(const void* q, void* out, int dtype, const void* pages, const int32_t* block_table, int max_pages, int page_size,
+                                     int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* positions, const int32_t* slots,
+                                     const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc, int window, int keep_first,
+                                     float scale, int chunk, int out_f32, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (chunk < 0) return sb::fail("sb_masked_attention: chunk %d", chunk);
   if (H <= 0 || G <= 0 || H % G != 0) return sb::fail("sb_masked_attention: %d heads do not divide into %d key/value heads", H, G);
   if (D <= 0 || Dv <= 0 || D > 640 || Dv > 640) return sb::fail("sb_masked_attention: key size %d, value size %d (at most 640)", D, Dv);
   if (window < 0 || keep_first < 0) return sb::fail("sb_masked_attention: window %d, kept first tokens %d", window, keep_first);
   AttnParams p{q, out, pages, block_table, max_pages, page_size, page_stride, v_offset, head_stride, positions, slots, slopes, sinks,
-               H, G, D, Dv, Dc, window, keep_first, scale};
+               H, G, D, Dv, Dc, window, keep_first, scale, chunk, out_f32};
   const size_t smem = sizeof(float) * (D + kWarps * Dv + 2 * kWarps);
   const bool small = D <= 256 && Dv <= 256;
   if (dtype == 0) {
@@ -829,6 +841,14 @@ SB_EXPORT int sb_masked_attention(const void* q, void* out, int dtype, const voi
   return sb::check_launch("sb_masked_attention");
 }
 
+SB_EXPORT int sb_masked_attention(const void* q, void* out, int dtype, const void* pages, const int32_t* block_table, int max_pages, int page_size,
+                                  int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* positions, const int32_t* slots,
+                                  const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc, int window, int keep_first,
+                                  float scale, cudaStream_t stream) {
+  return sb_masked_attention_ex(q, out, dtype, pages, block_table, max_pages, page_size, page_stride, v_offset, head_stride, positions, slots, slopes,
+                                sinks, n, H, G, D, Dv, Dc, window, keep_first, scale, 0, 0, stream);
+}
+
 // The tensor-core form: whether it takes a shape, and the launch. Entries come from the step's records on the device (meta).
 SB_EXPORT int sb_masked_attention_tiles_supported(int H, int G, int D, int Dv, int Dc, int64_t v_offset) {
   if (G <= 0 || H % G != 0) return 0;
@@ -838,16 +858,17 @@ SB_EXPORT int sb_masked_attention_tiles_supported(int H, int G, int D, int Dv, i
   return heads && D % 16 == 0 && D >= 16 && Dv % 16 == 0 && Dv >= 16 && Dv <= 512 && Dv <= Dc && Dc % 8 == 0 && v_offset % 8 == 0 && stage <= 200 * 1024;
 }
 
-SB_EXPORT int sb_masked_attention_tiles(const void* q, void* out, const void* pages, const int32_t* block_table, int max_pages, int page_size,
-                                        int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* meta, int meta_stride, int entries,
-                                        const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc, int window, int keep_first,
-                                        float scale, cudaStream_t stream) {
+SB_EXPORT int sb_masked_attention_tiles_ex(const void* q, void* out, const void* pages, const int32_t* block_table, int max_pages, int page_size,
+                                           int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* meta, int meta_stride,
+                                           int entries, const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc,
+                                           int window, int keep_first, float scale, int chunk, int out_f32, cudaStream_t stream) {
   if (n <= 0 || entries <= 0) return 0;
+  if (chunk < 0) return sb::fail("sb_masked_attention_tiles: chunk %d", chunk);
   if (!sb_masked_attention_tiles_supported(H, G, D, Dv, Dc, v_offset))
     return sb::fail("sb_masked_attention_tiles: heads %d / %d, key size %d, value size %d are not a shape of the tensor-core form", H, G, D, Dv);
   if (window < 0 || keep_first < 0) return sb::fail("sb_masked_attention_tiles: window %d, kept first tokens %d", window, keep_first);
   TileParams p{static_cast<const bf16*>(q), static_cast<bf16*>(out), static_cast<const bf16*>(pages), block_table, max_pages, page_size, page_stride,
-               v_offset, head_stride, meta, meta_stride, entries, slopes, sinks, H, G, D, Dv, Dc, window, keep_first, scale, 2};
+               v_offset, head_stride, meta, meta_stride, entries, slopes, sinks, H, G, D, Dv, Dc, window, keep_first, scale, 2, chunk, out_f32};
   const int groups = (Dv / 16 + 3) / 4;
   switch (groups) {
     case 1: return launch_tiles<1>(p, n, stream);
@@ -855,6 +876,14 @@ SB_EXPORT int sb_masked_attention_tiles(const void* q, void* out, const void* pa
     case 3: case 4: return launch_tiles<4>(p, n, stream);
     default: return launch_tiles<8>(p, n, stream);
   }
+}
+
+SB_EXPORT int sb_masked_attention_tiles(const void* q, void* out, const void* pages, const int32_t* block_table, int max_pages, int page_size,
+                                        int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* meta, int meta_stride, int entries,
+                                        const float* slopes, const float* sinks, int n, int H, int G, int D, int Dv, int Dc, int window, int keep_first,
+                                        float scale, cudaStream_t stream) {
+  return sb_masked_attention_tiles_ex(q, out, pages, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta, meta_stride, entries,
+                                      slopes, sinks, n, H, G, D, Dv, Dc, window, keep_first, scale, 0, 0, stream);
 }
 
 // ------------------------------------------------------------------ operations of the native step program (step_ops.h)
@@ -903,23 +932,225 @@ SB_EXPORT int sb_op_head_linear(const SbOp* op, const SbStep* s, void* stream) {
 }
 
 // i: 0 q, 1 out, 2 dtype, 3 pages, 4 block table, 5 max_pages, 6 page_size, 7 page_stride, 8 v_offset, 9 head_stride, 10 slopes, 11 sinks, 12 H,
-//    13 G, 14 D, 15 Dv, 16 Dc, 17 window, 18 keep_first      f: 0 scale
+//    13 G, 14 D, 15 Dv, 16 Dc, 17 window, 18 keep_first, 19 chunk, 20 the result as float32      f: 0 scale
 SB_EXPORT int sb_op_masked_attention(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
-  return sb_masked_attention(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], ptr<const void>(op->i[3]), ptr<const int32_t>(op->i[4]),
+  return sb_masked_attention_ex(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], ptr<const void>(op->i[3]), ptr<const int32_t>(op->i[4]),
                              (int)op->i[5], (int)op->i[6], op->i[7], op->i[8], op->i[9], positions(s), slots(s), ptr<const float>(op->i[10]),
                              ptr<const float>(op->i[11]), s->n, (int)op->i[12], (int)op->i[13], (int)op->i[14], (int)op->i[15], (int)op->i[16],
-                             (int)op->i[17], (int)op->i[18], (float)op->f[0], static_cast<cudaStream_t>(stream));
+                             (int)op->i[17], (int)op->i[18], (float)op->f[0], (int)op->i[19], (int)op->i[20], static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 q, 1 out, 2 pages, 3 block table, 4 max_pages, 5 page_size, 6 page_stride, 7 v_offset, 8 head_stride, 9 slopes, 10 sinks, 11 H, 12 G, 13 D,
-//    14 Dv, 15 Dc, 16 window, 17 keep_first      f: 0 scale
+//    14 Dv, 15 Dc, 16 window, 17 keep_first, 18 chunk, 19 the result as float32      f: 0 scale
 SB_EXPORT int sb_op_masked_attention_tiles(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
-  return sb_masked_attention_tiles(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), ptr<const int32_t>(op->i[3]), (int)op->i[4],
+  return sb_masked_attention_tiles_ex(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), ptr<const int32_t>(op->i[3]), (int)op->i[4],
                                    (int)op->i[5], op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, s->entries, ptr<const float>(op->i[9]),
                                    ptr<const float>(op->i[10]), s->n, (int)op->i[11], (int)op->i[12], (int)op->i[13], (int)op->i[14], (int)op->i[15],
-                                   (int)op->i[16], (int)op->i[17], (float)op->f[0], static_cast<cudaStream_t>(stream));
+                                   (int)op->i[16], (int)op->i[17], (float)op->f[0], (int)op->i[18], (int)op->i[19], static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// The general preparation of a step's queries, keys and values in front of the attention kernels above, and the gates behind them.
+//
+// `qkv_prepare_kernel`: a block per token. The row q | k | v of the projection (its K ranges' partial sums folded, bias added) waits in
+// shared memory; then, as the parameters say: an RMS norm of q and of k, over the whole projection (gains of that size) or per head
+// (one gain of the head's size for all heads); rotation of the first `rot` elements of every q and k head by the token's position, pairs
+// (2i, 2i + 1) or (i, i + rot / 2); a factor on q that grows with the position, 1 + c ln(floor((p + 1) / every) + 1); q stored, k and v
+// appended to the token's page row. All in 32-bit.
+//
+// `head_gate_kernel`: the attention's result (float32 [n][heads][Dv]) times a gate that is a column range of the projection's partial
+// sums, sigmoid applied: one gate per element, or one per head. With two maps per head (differential attention) the result of map 1 less
+// lambda times that of map 2 is RMS-normed over the head's values (no gain) and multiplied by a constant first.
+namespace {
+
+struct PrepareParams {
+  const float* proj;         // [P][n][width]: q (Hq D) | k (Hkv D) | v (Hkv Dv) | whatever else the projection carries
+  int n_partials;
+  int64_t partial_stride;
+  int width;
+  const float* bias;         // [Hq D + Hkv D + Hkv Dv] or null
+  const float* q_gain;       // norm_mode 1: [Hq D]; 2: [D]
+  const float* k_gain;       // norm_mode 1: [Hkv D]; 2: [D]
+  int norm_mode;             // 0: none, 1: over the whole projection, 2: per head
+  float eps;
+  const float* cos_sin;      // [positions][rot / 2][2]
+  int rot, interleaved;
+  float temp_coef;
+  int temp_every;            // 0: no factor on q
+  const int32_t* positions;
+  const int32_t* slots;
+  void* q_out;               // [n][Hq D]
+  PageRef c;
+  int Hq, Hkv, D, Dv;
+  int write_kv;
+};
+
+template <class T>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(PrepareParams p) {
+  extern __shared__ float row_values[];
+  __shared__ float red[32];
+  sb::grid_launch_dependents();
+  const int row = blockIdx.x;
+  const int nq = p.Hq * p.D, nk = p.Hkv * p.D, cols = nq + nk + p.Hkv * p.Dv;
+  const int pos = p.positions[row], slot = p.slots[row];
+  const int page = p.write_kv ? p.c.block_table[static_cast<int64_t>(slot) * p.c.max_pages + pos / p.c.page_size] : 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  sb::grid_dependency_wait();
+  const float* src = p.proj + static_cast<int64_t>(row) * p.width;
+  float sq_q = 0.0f, sq_k = 0.0f;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = folded(src + i, p.n_partials, p.partial_stride);
+    if (p.bias != nullptr) v = __fadd_rn(v, p.bias[i]);
+    row_values[i] = v;
+    if (i < nq) sq_q = fmaf(v, v, sq_q);
+    else if (i < nq + nk) sq_k = fmaf(v, v, sq_k);
+  }
+  if (p.norm_mode == 1) {
+    const float rq = 1.0f / sqrtf(sb::block_sum(sq_q, red) / static_cast<float>(nq) + p.eps);
+    const float rk = 1.0f / sqrtf(sb::block_sum(sq_k, red) / static_cast<float>(nk) + p.eps);
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x)
+      row_values[i] = i < nq ? __fmul_rn(__fmul_rn(row_values[i], rq), p.q_gain[i]) : __fmul_rn(__fmul_rn(row_values[i], rk), p.k_gain[i - nq]);
+  } else if (p.norm_mode == 2) {
+    __syncthreads();
+    for (int hh = warp; hh < p.Hq + p.Hkv; hh += warps) {      // a warp per head: the squares by lane in ascending elements, then xor shuffles
+      float* head = row_values + hh * p.D;
+      float ss = 0.0f;
+      for (int d = lane; d < p.D; d += 32) ss = fmaf(head[d], head[d], ss);
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = 1.0f / sqrtf(ss / static_cast<float>(p.D) + p.eps);
+      const float* gain = hh < p.Hq ? p.q_gain : p.k_gain;
+      for (int d = lane; d < p.D; d += 32) head[d] = __fmul_rn(__fmul_rn(head[d], r), gain[d]);
+    }
+  }
+  __syncthreads();
+  float temp = 1.0f;
+  if (p.temp_every > 0) temp = fmaf(p.temp_coef, logf(static_cast<float>((pos + 1) / p.temp_every) + 1.0f), 1.0f);
+  const int rh = p.rot / 2;
+  T* pages = static_cast<T*>(p.c.pages);
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = row_values[i];
+    const bool is_v = i >= nq + nk;
+    if (!is_v) {
+      const int d = i % p.D;
+      if (d < p.rot) {
+        int pair, other;
+        bool low;
+        if (p.interleaved) pair = d >> 1, low = (d & 1) == 0, other = low ? i + 1 : i - 1;
+        else low = d < rh, pair = low ? d : d - rh, other = low ? i + rh : i - rh;
+        const float b = row_values[other];
+        const float2 cs = *reinterpret_cast<const float2*>(p.cos_sin + (static_cast<int64_t>(pos) * rh + pair) * 2);
+        v = low ? __fsub_rn(__fmul_rn(v, cs.x), __fmul_rn(b, cs.y)) : __fadd_rn(__fmul_rn(v, cs.x), __fmul_rn(b, cs.y));
+      }
+    }
+    if (i < nq) {
+      static_cast<T*>(p.q_out)[static_cast<int64_t>(row) * nq + i] = sb::narrow<T>(__fmul_rn(v, temp));
+    } else if (p.write_kv) {
+      const int e = is_v ? i - nq - nk : i - nq;
+      const int dim = is_v ? p.Dv : p.D, head = e / dim, d = e % dim;
+      pages[static_cast<int64_t>(page) * p.c.page_stride + (is_v ? p.c.v_offset : 0) + static_cast<int64_t>(head) * p.c.head_stride +
+            static_cast<int64_t>(pos % p.c.page_size) * p.c.Dc + d] = sb::narrow<T>(v);
+    }
+  }
+}
+
+struct HeadGateParams {
+  const float* a;            // [n][maps H][Dv]: with two maps, map m of head h = g Hg + j lies at head (2 g + m) Hg + j (Hg = H / G)
+  const float* proj;         // the gate's partial sums [P][n][width], columns g_off ..
+  int n_partials;
+  int64_t partial_stride;
+  int width, g_off;
+  void* out;                 // [n][H Dv]
+  int H, G, Dv, maps;
+  int per_head;              // 1: one gate per head, 0: one per element
+  float lambda, post, eps;   // two maps: (a1 - lambda a2) RMS-normed, times post
+};
+
+template <class T>
+__global__ void __launch_bounds__(128) head_gate_kernel(HeadGateParams p) {
+  sb::grid_launch_dependents();
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int Hg = p.H / p.G;
+  sb::grid_dependency_wait();
+  const float* gate = p.proj + static_cast<int64_t>(row) * p.width + p.g_off;
+  T* out = static_cast<T*>(p.out) + static_cast<int64_t>(row) * p.H * p.Dv;
+  for (int h = warp; h < p.H; h += warps) {
+    const int g = h / Hg, j = h % Hg;
+    const float* a1 = p.a + (static_cast<int64_t>(row) * p.maps * p.H + (p.maps == 2 ? (2 * g) * Hg + j : h)) * p.Dv;
+    const float* a2 = a1 + static_cast<int64_t>(Hg) * p.Dv;
+    float scale = 1.0f;
+    if (p.maps == 2) {
+      float ss = 0.0f;
+      for (int d = lane; d < p.Dv; d += 32) {
+        const float o = __fsub_rn(a1[d], __fmul_rn(p.lambda, a2[d]));
+        ss = fmaf(o, o, ss);
+      }
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      scale = p.post / sqrtf(ss / static_cast<float>(p.Dv) + p.eps);
+    }
+    float head_gate = 0.0f;
+    if (p.per_head) head_gate = 1.0f / (1.0f + expf(-folded(gate + h, p.n_partials, p.partial_stride)));
+    for (int d = lane; d < p.Dv; d += 32) {
+      float o = p.maps == 2 ? __fmul_rn(__fsub_rn(a1[d], __fmul_rn(p.lambda, a2[d])), scale) : a1[d];
+      const float gt = p.per_head ? head_gate : 1.0f / (1.0f + expf(-folded(gate + h * p.Dv + d, p.n_partials, p.partial_stride)));
+      out[h * p.Dv + d] = sb::narrow<T>(__fmul_rn(o, gt));
+    }
+  }
+}
+
+}  // namespace
+
+// i: 0 projection partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 bias, 5 q gain, 6 k gain, 7 norm mode,
+//    8 cos_sin, 9 rot, 10 interleaved pairs, 11 temp_every, 12 q out, 13 dtype, 14 pages, 15 block table, 16 max_pages, 17 page_size,
+//    18 page_stride, 19 v_offset, 20 head_stride, 21 Hq, 22 Hkv, 23 D, 24 Dv, 25 Dc, 26 write_kv
+// f: 0 eps, 1 temp_coef
+SB_EXPORT int sb_op_qkv_prepare(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[1], Hq = (int)op->i[21], Hkv = (int)op->i[22], D = (int)op->i[23], Dv = (int)op->i[24];
+  const int rot = (int)op->i[9], mode = (int)op->i[7], dtype = (int)op->i[13];
+  const int64_t cols = static_cast<int64_t>(Hq) * D + static_cast<int64_t>(Hkv) * (D + Dv);
+  if (Hq <= 0 || Hkv <= 0 || D <= 0 || Dv <= 0 || cols > width) return sb::fail("sb_op_qkv_prepare: heads %d / %d, sizes %d / %d, row %d", Hq, Hkv, D, Dv, width), SB_OP_FAILED;
+  if (rot < 0 || rot % 2 != 0 || rot > D) return sb::fail("sb_op_qkv_prepare: %d rotated elements of %d", rot, D), SB_OP_FAILED;
+  if (mode < 0 || mode > 2) return sb::fail("sb_op_qkv_prepare: norm mode %d", mode), SB_OP_FAILED;
+  PrepareParams p{ptr<const float>(op->i[0]), partial_count(op->i[2], op->i[3], s->n), static_cast<int64_t>(s->n) * width, width,
+                  ptr<const float>(op->i[4]), ptr<const float>(op->i[5]), ptr<const float>(op->i[6]), mode, (float)op->f[0],
+                  ptr<const float>(op->i[8]), rot, (int)op->i[10], (float)op->f[1], (int)op->i[11], positions(s), slots(s), ptr<void>(op->i[12]),
+                  page_ref(ptr<void>(op->i[14]), ptr<const int32_t>(op->i[15]), (int)op->i[16], (int)op->i[17], op->i[18], op->i[19], op->i[20],
+                           (int)op->i[25]),
+                  Hq, Hkv, D, Dv, (int)op->i[26]};
+  const size_t smem = static_cast<size_t>(cols) * sizeof(float);
+  if (smem > 160 * 1024) return sb::fail("sb_op_qkv_prepare: a row of %lld elements does not fit the row buffer", (long long)cols), SB_OP_FAILED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(qkv_prepare_kernel<float>, dim3(s->n), dim3(256), smem, st, p);
+  } else if (dtype == 1) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(qkv_prepare_kernel<bf16>, dim3(s->n), dim3(256), smem, st, p);
+  } else {
+    return sb::fail("sb_op_qkv_prepare: unsupported dtype %d", dtype), SB_OP_FAILED;
+  }
+  return sb::check_launch("sb_op_qkv_prepare");
+}
+
+// i: 0 attention result (float32), 1 gate's partial sums (flat), 2 their width, 3 K ranges S, 4 most tokens with a buffer per range, 5 g_off,
+//    6 out, 7 out dtype, 8 H, 9 G, 10 Dv, 11 maps, 12 one gate per head
+// f: 0 lambda, 1 factor behind the norm, 2 eps
+SB_EXPORT int sb_op_head_gate(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  const int width = (int)op->i[2], H = (int)op->i[8], G = (int)op->i[9], maps = (int)op->i[11];
+  if (H <= 0 || G <= 0 || H % G != 0 || maps < 1 || maps > 2) return sb::fail("sb_op_head_gate: heads %d / %d, maps %d", H, G, maps), SB_OP_FAILED;
+  HeadGateParams p{ptr<const float>(op->i[0]), ptr<const float>(op->i[1]), partial_count(op->i[3], op->i[4], s->n), static_cast<int64_t>(s->n) * width,
+                   width, (int)op->i[5], ptr<void>(op->i[6]), H, G, (int)op->i[10], maps, (int)op->i[12], (float)op->f[0], (float)op->f[1],
+                   (float)op->f[2]};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (op->i[7] == 0) sb::launch_pdl(head_gate_kernel<float>, dim3(s->n), dim3(128), 0, st, p);
+  else if (op->i[7] == 1) sb::launch_pdl(head_gate_kernel<bf16>, dim3(s->n), dim3(128), 0, st, p);
+  else return sb::fail("sb_op_head_gate: unsupported dtype %d", (int)op->i[7]), SB_OP_FAILED;
+  return sb::check_launch("sb_op_head_gate");
 }

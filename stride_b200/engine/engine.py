@@ -28,7 +28,7 @@ from ..config import resolve_architecture
 from ..kernels.build import build_all
 from ..kernels.native import NotNative, StepProgram
 from ..parts import BuildEnv, DecoderModel, StepContext, Workspace
-from ..weights.loader import check_plan, load_weights
+from ..weights.loader import check_plan, load_weights, tensor_shapes
 
 
 class EngineError(RuntimeError):
@@ -103,6 +103,9 @@ class Engine:
             config = json.loads(cfg_path.read_text())
         self.config_dict = config
         self.architecture = resolve_architecture(config)
+        if self.architecture.complete_config is not None:      # sizes that config.json leaves to the tensors' shapes
+            shapes = {n: tuple(t.shape) for n, t in tensors.items()} if tensors is not None else tensor_shapes(model_dir)
+            config = self.architecture.complete_config(config, shapes)
         self.config = self.architecture.parse_config(config)
         self.spec = self.architecture.model_spec(self.config)
         self.max_context = o.max_context or self.spec.max_positions

@@ -49,6 +49,7 @@ SOURCES = {
     "masked_attention": "masked_attention.cu",
     "gated_recurrence": "gated_recurrence.cu",
     "rglru": "rglru.cu",
+    "delta_rule": "delta_rule.cu",
     "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-g1", "-shared", "-fPIC", "-fvisibility=hidden"]

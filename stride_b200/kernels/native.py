@@ -271,3 +271,82 @@ class StepProgram:
         if rc != 0:
             k = self._failed.value
             raise RuntimeError(f"operation {k} of the step failed: " + library(self._libraries[k]).sb_last_error().decode(errors="replace"))
+
+
+class ImmediateProgram:
+    """A step program that launches every operation the moment it is added, on the current torch stream, for the step that a
+    `StepContext` describes. A part that has written its share of a step once, as `emit(program, ...)`, gets its `forward(ctx, ...)` from
+    it: `with ImmediateProgram(ctx, stream) as program: self.emit(program, ...)`. The operations are the very functions the native
+    runner calls, with the same arguments, so the two drivers launch the same kernels.
+
+    The context's integer inputs must lie in one device buffer in the layout of `SbStep` (tokens, positions, slots, wanted rows,
+    entry records, each `max_rows` apart), which is how the engine stages them."""
+
+    def __init__(self, ctx, stream, sampled=None):
+        self.workspace = ctx.workspace
+        self._stream = stream
+        self._few = ops.gemm_tc_partial_tokens() if ctx.compute_dtype == torch.bfloat16 else 0
+        self.few_tokens = self._few
+        base = ctx.token_ids.data_ptr()
+        R = (ctx.positions.data_ptr() - base) // 4
+        if R <= 0 or ctx.slots.data_ptr() != base + 8 * R or (ctx.entry_meta is not None and ctx.entry_meta.data_ptr() != base + 16 * R):
+            raise NotNative("the step's integer inputs do not lie in one buffer in the step program's layout")
+        self.max_rows = R
+        self.step = SbStep()
+        self.step.n, self.step.entries, self.step.wanted = ctx.n, len(ctx.entry_length), 0
+        self.step.static_keys, self.step.max_rows, self.step.n_plans, self.step.ints = ctx.static_keys, R, 0, base
+        self.sampled = ctx.sampled if sampled is None else sampled
+        self.embedding_output = ctx.embedding_output
+        self._h, self.h_touched, self.pending = None, False, None
+        self.chain = None
+
+    def __enter__(self):
+        p = self._stream.take_pending() if self._stream is not None else None
+        if p is not None:
+            self.pending = (p, p.shape[0], p.shape[2])
+        return self
+
+    def __exit__(self, kind, value, trace):
+        if kind is None and self._stream is not None and self.pending is not None:
+            flat, S, M = self.pending
+            n = self.step.n
+            P = S if (S > 1 and n <= self._few) else 1
+            self._stream.set_pending(flat.reshape(-1)[:P * n * M].view(P, n, M))
+            self.pending = None
+        return False
+
+    @property
+    def h(self):
+        self.h_touched = True
+        return self._h if self._h is not None else self._stream.h
+
+    @h.setter
+    def h(self, buffer):
+        self._h, self.h_touched = buffer, False
+
+    def take_pending(self):
+        p, self.pending = self.pending, None
+        return p
+
+    def need_folded(self, who: str) -> None:
+        if self.pending is not None:
+            raise NotNative(f"{who} adds to the residual stream while partial sums are pending on it")
+
+    def add(self, library_name: str, function: str, ints, floats=(), chain=None) -> None:
+        if len(ints) > OP_INTS or len(floats) > OP_FLOATS:
+            raise ValueError(f"{function}: too many arguments for one operation")
+        lib = library(library_name)
+        fn = getattr(lib, function)
+        if not getattr(fn, "_sb_typed", False):
+            fn.restype, fn.argtypes = c_int, [ctypes.POINTER(SbOp), ctypes.POINTER(SbStep), c_void_p]
+            fn._sb_typed = True
+        op = SbOp()
+        for k, v in enumerate(ints):
+            op.i[k] = _value(v)
+        for k, v in enumerate(floats):
+            op.f[k] = float(v)
+        rc = fn(ctypes.byref(op), ctypes.byref(self.step), ops._stream())
+        if rc == 1:
+            raise RuntimeError(f"{function}: " + lib.sb_last_error().decode(errors="replace"))
+        if rc == 0:
+            ops.launches += 1

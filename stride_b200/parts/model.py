@@ -110,6 +110,7 @@ class DecoderModel:
         has no native form."""
         ws, H = program.workspace, self.spec.hidden_size
         program.h = ws.get("model.h", ws.max_tokens, (H,), torch.float32)
+        program.sampled = sampled          # parts that look a token up again (a per-layer token input) read placeholders from here
         if self.keeps_embedding:
             program.embedding_output = ws.get("model.embedding_output", ws.max_tokens, (H,), torch.float32)
             self.embedding.emit(program, program.h, sampled, program.embedding_output)

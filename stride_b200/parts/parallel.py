@@ -67,3 +67,59 @@ class ParallelMixer(Mixer):
 
     def emit(self, program, x, cache):
         emit_fold(program, self.emit_sources(program, x, cache), None, self.hidden)
+
+
+@register_part("mixer", "parallel_normed")
+class NormedParallelMixer(Mixer):
+    """Two mixers side by side whose results are each RMS-normed over the model width, with a gain of its own, before their weighted sum:
+    r = c_0 g_0 * m_0(x) / rms(m_0(x)) + c_1 g_1 * m_1(x) / rms(m_1(x)). params: hidden_size, members (two PartSpecs of category "mixer"),
+    scales (a constant per member), eps. tensors: norms (the two gains' names)."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.eps = int(spec.params["hidden_size"]), float(spec.params["eps"])
+        members = list(spec.params["members"])
+        self.scales = [float(c) for c in spec.params["scales"]]
+        if len(members) != 2 or len(self.scales) != 2 or len(spec.tensors["norms"]) != 2:
+            raise ValueError("parallel mixer with norms: two members, two constants and two gains")
+        self.members = [part_class("mixer", m.kind)(m, env) for m in members]
+        self.graph_safe = all(m.graph_safe for m in self.members)
+        self.gains = None
+
+    def tensor_plan(self):
+        from .spec import TensorPlan
+        plan = {name: TensorPlan((self.hidden,)) for name in self.spec.tensors["norms"]}
+        for m in self.members:
+            plan.update(m.tensor_plan())
+        return plan
+
+    def bind(self, tensors):
+        for m in self.members:
+            m.bind(tensors)
+        self.gains = [tensors[name].to(torch.float32).contiguous() for name in self.spec.tensors["norms"]]
+
+    def weight_bytes(self):
+        return sum(m.weight_bytes() for m in self.members)
+
+    def cache_need(self):
+        return [m.cache_need() for m in self.members]
+
+    def kernel_libraries(self):
+        return set().union({"branch"}, *(m.kernel_libraries() for m in self.members))
+
+    def forward(self, ctx, x, stream, cache):
+        from ..kernels.native import ImmediateProgram
+        with ImmediateProgram(ctx, stream) as program:
+            self.emit(program, x, cache)
+
+    def emit(self, program, x, cache):
+        ws = program.workspace
+        buffers = [ws.get(f"parallel.branch{k}", ws.max_tokens, (self.hidden,), torch.float32) for k in range(2)]
+        (a, pa), (b, pb) = [emit_on_branch(program, buf, lambda m=m, c=c: m.emit(program, x, c))
+                            for m, buf, c in zip(self.members, buffers, cache.parts)]
+        (fa, Sa, _), (fb, Sb, _) = pa or (None, 1, 0), pb or (None, 1, 0)
+        program.need_folded("mixers side by side")
+        program.add("branch", "sb_op_branch_pair_norm_fold",
+                    [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, self.gains[0], self.gains[1], self.gains[0].dtype, self.hidden],
+                    [self.scales[0], self.scales[1], self.eps])

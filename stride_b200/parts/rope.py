@@ -40,6 +40,23 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: dict) -> np.ndar
     return inv
 
 
+def rescaled_long_waves(inv: np.ndarray, scaling: dict) -> np.ndarray:
+    """The "llama3" rescaling in 64-bit: a pair whose wave is shorter than original / high keeps its frequency, one whose wave is longer than
+    original / low turns `factor` times slower, and between the two the frequencies are blended, with the weight
+    s = (original / wave - low) / (high - low) on the unscaled one."""
+    factor, orig = float(scaling["factor"]), float(scaling["original_max_position_embeddings"])
+    low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+    out = inv.copy()
+    for i, f in enumerate(inv):
+        wave = 2.0 * math.pi / f
+        if wave > orig / low:
+            out[i] = f / factor
+        elif not wave < orig / high:
+            s = (orig / wave - low) / (high - low)
+            out[i] = (1.0 - s) * f / factor + s * f
+    return out
+
+
 def yarn_frequencies(rotary_dim: int, theta: float, factor: float, original: float, fast: float, slow: float):
     """YaRN: pairs that complete more than `fast` turns over `original` positions keep their frequency, pairs that complete fewer than
     `slow` turns are slowed by `factor`, and in between a ramp over the pair index blends the two. Pair i of frequency
@@ -63,8 +80,9 @@ def yarn_frequencies(rotary_dim: int, theta: float, factor: float, original: flo
 @register_part("position", "rope")
 class RotaryEncoding(PositionEncoding):
     """params: head_dim, rotary_dim (default head_dim), theta, scaling (dict with rope_type and its factors),
-    exact_angles (False by default: frequencies and angles in 32-bit as above; True: frequency theta^(-2i/rotary_dim) and
-    angle in 64-bit, so that the table is the rounding of the exact cos and sin at every position). The scaling
+    exact_angles (False by default: frequencies and angles in 32-bit as above; True: frequency theta^(-2i/rotary_dim), with the
+    llama3 rescaling of long waves if the scaling asks for it, and angle in 64-bit, so that the table is the rounding of the exact cos and
+    sin at every position). The scaling
     {"rope_type": "yarn", factor, original, fast, slow} (`yarn_frequencies`) is always made in 64-bit, and its factor on cos and sin
     is part of the table."""
     graph_safe = True
@@ -84,9 +102,12 @@ class RotaryEncoding(PositionEncoding):
                                               float(sc["slow"]))
             angle = inv[None, :] * np.arange(env.max_positions, dtype=np.float64)[:, None]
         elif p.get("exact_angles"):
-            if (p.get("scaling") or {}).get("rope_type", "default") != "default":
-                raise ValueError("rotary encoding: exact_angles goes with the default scaling only")
             inv = np.array([math.pow(float(p["theta"]), -2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)], dtype=np.float64)
+            kind = (p.get("scaling") or {}).get("rope_type", "default")
+            if kind == "llama3":
+                inv = rescaled_long_waves(inv, p["scaling"])
+            elif kind != "default":
+                raise ValueError(f"rotary encoding: exact_angles goes with the default and the llama3 scaling, not '{kind}'")
             angle = inv[None, :] * np.arange(env.max_positions, dtype=np.float64)[:, None]
         else:
             inv = inverse_frequencies(self.rotary_dim, float(p["theta"]), p.get("scaling") or {})

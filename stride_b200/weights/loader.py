@@ -80,6 +80,16 @@ def _open_files(model_dir) -> dict:
     return where
 
 
+def tensor_shapes(model_dir) -> dict:
+    """name -> shape of every tensor of the model folder, from the files' headers alone."""
+    where = _open_files(model_dir)
+    try:
+        return {n: tuple(f.shape(n)) for n, f in where.items()}
+    finally:
+        for f in {id(f): f for f in where.values()}.values():
+            f.close()
+
+
 def load_weights(model_dir, plan: dict, device) -> dict:
     """Read the model folder's safetensors (one file or shards), check them against `plan`, return name -> device tensor."""
     where = _open_files(model_dir)
