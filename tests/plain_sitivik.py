@@ -50,7 +50,9 @@ def frequencies(rot: dict):
 
 
 def rotate(x, positions, rot: dict, interleaved: bool):
-    """x [T, heads, dim]: the first rot.dims elements of every head turned by the position's angles."""
+    """x [T, heads, dim]: the first rot.dims elements of every head turned by the position's angles (no `rot`: nothing is turned)."""
+    if not rot:
+        return x
     dims = rot["dims"]
     a = positions.to(F)[:, None] * frequencies(rot)[None, :]        # [T, dims / 2]
     c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
@@ -114,18 +116,18 @@ def windowed_left(w, p, m, h, eps, bf16):
     q, k, v = linear(w, p + "q", h, bf16), linear(w, p + "k", h, bf16), linear(w, p + "v", h, bf16)
     q = rms(q, eps) * w[p + "q.norm"]
     k = rms(k, eps) * w[p + "k.norm"]
-    q = rotate(q.view(T, H, D), pos, m["rot"], True)
-    k = rotate(k.view(T, G, D), pos, m["rot"], True)
+    q = rotate(q.view(T, H, D), pos, m.get("rot"), True)
+    k = rotate(k.view(T, G, D), pos, m.get("rot"), True)
     o = softmax_attention(rnd(q, bf16), rnd(k, bf16), rnd(v.view(T, G, Dv), bf16), m["scale"], window_mask(T, m["mask"]["size"]), False)
-    o = rnd(o, bf16).reshape(T, H * Dv) * torch.sigmoid(linear(w, p + "g", h, bf16))
+    o = o.reshape(T, H * Dv) * torch.sigmoid(linear(w, p + "g", h, bf16))
     return linear(w, p + "o", o, bf16)
 
 
 def retention_right(w, p, m, h, eps, bf16):
     T, H, D, Dv = h.shape[0], m["heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
-    q = rotate(linear(w, p + "q", h, bf16).view(T, H, D), pos, m["rot"], False)
-    k = rotate(linear(w, p + "k", h, bf16).view(T, H, D), pos, m["rot"], False) * D ** -0.5
+    q = rotate(linear(w, p + "q", h, bf16).view(T, H, D), pos, m.get("rot"), False)
+    k = rotate(linear(w, p + "k", h, bf16).view(T, H, D), pos, m.get("rot"), False) * D ** -0.5
     v = linear(w, p + "v", h, bf16).view(T, H, Dv)
     o = torch.zeros(T, H, Dv, dtype=F)
     for hd in range(H):
@@ -169,9 +171,9 @@ def chunked_left(w, p, m, h, eps, bf16):
     q = rms(linear(w, p + "q", h, bf16).view(T, H, D), eps) * w[p + "q.norm"]
     k = rms(linear(w, p + "k", h, bf16).view(T, G, D), eps) * w[p + "k.norm"]
     v = linear(w, p + "v", h, bf16).view(T, G, Dv)
-    q, k = rotate(q, pos, m["rot"], True), rotate(k, pos, m["rot"], True)
+    q, k = rotate(q, pos, m.get("rot"), True), rotate(k, pos, m.get("rot"), True)
     o = softmax_attention(rnd(q, bf16), rnd(k, bf16), rnd(v, bf16), m["scale"], chunk_mask(T, m["mask"]["size"]), True)
-    o = rnd(o, bf16).reshape(T, H * Dv) * torch.sigmoid(linear(w, p + "g", h, bf16))
+    o = o.reshape(T, H * Dv) * torch.sigmoid(linear(w, p + "g", h, bf16))
     return linear(w, p + "o", o, bf16)
 
 
