@@ -239,11 +239,13 @@ def test_token_side_and_normed_pair_against_the_plain_functions(sitivik_dirs):
             fed[4] = -1                                                  # a token still being chosen: read from the request's slot
             st = _Step([(1, 0, n, 0)], dtype, ws, tokens=fed)
             st.ctx.sampled = torch.tensor([0, toks[4], 0], dtype=torch.int32, device=DEV)
-            pending = (torch.randn(2, n, W, generator=g) * 0.1)
+            # (only the bfloat16 engine's projections leave partial sums pending on the stream)
+            pending = torch.randn(2, n, W, generator=g) * (0.1 if dtype == torch.bfloat16 else 0.0)
             h = ws.get("model.h", n, (W,), torch.float32)
             h.copy_((x - pending.sum(0)).to(DEV))
             stream = ResidualStream(h)
-            stream.set_pending(pending.to(DEV))
+            if dtype == torch.bfloat16:
+                stream.set_pending(pending.to(DEV))
             part.forward(st.ctx, stream)
             stream.fold()
             x64 = (x - pending.sum(0)).double() + pending.double().sum(0)
@@ -391,11 +393,11 @@ def test_window_and_chunk_edges_show_and_agree(sitivik_dirs):
     toks = random_tokens(cfg["vocab"], 90, 77)
     want = plain.forward(cfg, w, toks).float()
     tol = logit_tolerance("float32", want)
-    for layer, delta in ((1, 1), (1, -1), (2, 1), (2, -1), (3, -1)):
+    for layer, delta, least in ((1, 1, 20), (1, -1, 20), (2, 1, 20), (2, -1, 20), (3, -1, 5), (3, 1, 5)):     # (the last layer's window is 40 keys wide)
         other = copy.deepcopy(cfg)
         other["layers"][layer]["mixer"]["left"]["mask"]["size"] += delta
         moved = (plain.forward(other, w, toks).float() - want).abs().max(dim=1).values
-        assert moved[45:].min() > 20 * tol, f"the yardstick does not notice layer {layer}'s mask {delta:+d}"
+        assert moved[45:].min() > least * tol, f"the yardstick does not notice layer {layer}'s mask {delta:+d}"
     eng = _engine(sitivik_dirs["XU"], "float32", 16, 12)
     slot = eng.cache.acquire_slot()
     eng.cache.ensure(slot, 50)
