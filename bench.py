@@ -367,6 +367,27 @@ def _pusisun_config(width: int, ff: int, vocab: int, pairs: int, window: int) ->
     return {"architecture": "Pusisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": [att, lat] * pairs}
 
 
+def _sitivik_config(width: int, ff: int, vocab: int, pairs: int, window: int) -> dict:
+    """Four layers: (windowed attention beside retention), differential attention, (windowed attention beside retention), (chunked
+    attention with a sink beside the gated delta rule), each with a gated feed-forward of `ff` and a per-layer token input of 256: the
+    windowed and chunked attentions have the heads of the Llama 3.2 1B layer, the differential attention 16 heads of two maps of 64 over
+    values of 128, retention and the delta rule 16 heads of 128 x 128 (the delta rule with four taps and low-rank projections of 64)."""
+    mlp = {"kind": "dense", "ff": ff}
+    left = {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": window}}
+    heads = width // 128
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": dict(left, rot={"dims": 64, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}),
+                     "right": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+                               "decay": [1.0 - 2.0 ** (-3 - 5.0 * h / max(heads - 1, 1)) for h in range(heads)]}}}
+    dif = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5, "q_temp": {"coef": 0.1, "every": 256}}}
+    par2 = {"type": "parallel_2", "mlp": mlp,
+            "mixer": {"left": dict(left, rot={"dims": 32, "base": 500000.0}), "left_scale": 1.0, "right_scale": 1.0,
+                      "right": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}}}
+    return {"architecture": "Sitivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "token_side": {"dim": 256},
+            "layers": ([par, dif] * pairs)[:2 * pairs - 1] + [par2]}
+
+
 def design_compare(a) -> int:
     """Keralorn at layer sizes of a real model beside LlamaForCausalLM with as many layers of the same width, heads and
     feed-forward (random weights, bfloat16 engine): a prompt of 2,048 tokens in one step, decode steps at batch 8 and 64
@@ -385,8 +406,11 @@ def design_compare(a) -> int:
         configs = {"ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), **configs}
     if a.design == "pusisun":      # beside the closest design (windowed attention of the same heads, routed experts of the same sizes) and Llama
         configs = {"pusisun": _pusisun_config(width, ff, vocab, pairs, 1024), "ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), "llama": llama}
+    if a.design == "sitivik":      # beside the closest design (windowed attention beside a gated linear attention with a state per request) and Llama
+        configs = {"sitivik": _sitivik_config(width, ff, vocab, pairs, 1024), "ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), "llama": llama}
     gen = torch.Generator().manual_seed(3)
-    out = {"design": a.design, "beside": {"keralorn": "LlamaForCausalLM", "ganupel": "Keralorn, LlamaForCausalLM", "pusisun": "Ganupel, LlamaForCausalLM"}[a.design], "width": width, "ff": ff, "layers": layers, "vocab": vocab,
+    out = {"design": a.design, "beside": {"keralorn": "LlamaForCausalLM", "ganupel": "Keralorn, LlamaForCausalLM", "pusisun": "Ganupel, LlamaForCausalLM",
+                                          "sitivik": "Ganupel, LlamaForCausalLM"}[a.design], "width": width, "ff": ff, "layers": layers, "vocab": vocab,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": pk,
            "l2": "weights and caches of a step exceed the 126 MB L2; the kernel timings flush L2 between launches"}
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
@@ -464,8 +488,8 @@ def design_compare(a) -> int:
         del eng
         torch.cuda.empty_cache()
 
-    if a.design in ("ganupel", "pusisun"):
-        out["kernels"] = (_ganupel_kernels if a.design == "ganupel" else _pusisun_kernels)(timed, pk, width, ff)
+    if a.design in ("ganupel", "pusisun", "sitivik"):
+        out["kernels"] = {"ganupel": _ganupel_kernels, "pusisun": _pusisun_kernels, "sitivik": _sitivik_kernels}[a.design](timed, pk, width, ff)
         out["clocks"] = clocks.stop()
         print(json.dumps(out))
         return 0
@@ -742,6 +766,146 @@ def _pusisun_kernels(timed, pk: dict, width: int, ff: int) -> dict:
     return kern
 
 
+def _sitivik_kernels(timed, pk: dict, width: int, ff: int) -> dict:
+    """Sitivik's own kernels alone (L2 flushed between launches), each beside the like kernel of Ganupel, Keralorn or Llama."""
+    import torch
+    from stride_b200.kernels import ops
+    from stride_b200.kernels.native import ImmediateProgram
+    from stride_b200.parts import Workspace
+    from stride_b200.parts.context import step_context
+    dev, kern, f32, bf = "cuda", {}, torch.float32, torch.bfloat16
+    hbm = pk["hbm_gbs"] * 1e9
+
+    def record(label, ms, moved=None, flops=None, **more):
+        r = {"ms": round(ms, 4)}
+        if moved is not None:
+            r.update(gb_s=round(moved / ms / 1e6, 1), hbm_fraction_of_measured=round(moved / (ms * 1e-3) / hbm, 3))
+        if flops is not None:
+            r.update(tflops=round(flops / ms / 1e9, 2), fraction_of_measured_bf16=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+        r.update(more)
+        kern[label] = r
+
+    ws = Workspace(dev, 2048)
+
+    def op(ctx, library, function, ints, floats=()):
+        """One operation of the step program, launched for the step `ctx` describes."""
+        return ImmediateProgram(ctx, None).prepared(library, function, ints, floats)
+
+    Hq, G, Dh, window, page = width // 64, width // 256, 64, 1024, 64
+    H, D, V = width // 128, 128, 128
+    cs = torch.rand(4096, 32, 2, device=dev)
+    for label, entries, length, past in (("prefill_2048", 1, 2048, 0), ("decode_b64", 64, 1, 1500)):
+        n, per = entries * length, (past + length + page - 1) // page
+        ctx = step_context([(e, length, past) for e in range(entries)], ws, bf, rows=2048)
+        pages = torch.randn(entries * per + 1, 2, G, page, Dh, device=dev).to(bf)
+        table = torch.arange(entries * per, dtype=torch.int32, device=dev).view(entries, per)
+        where = [per, page, pages.stride(0), pages.stride(1), pages.stride(2)]
+        q = torch.randn(n, Hq * Dh, device=dev).to(bf)
+        o32 = torch.empty(n, Hq * Dh, dtype=f32, device=dev)
+        sinks = torch.zeros(Hq, device=dev)
+        # windowed and chunked attention (the tile kernel of the masked attention with another mask), beside Ganupel's sigmoid attention
+        for name, win, chunk, sink in (("windowed", window, 0, None), ("chunked_sink", 0, window, sinks)):
+            lo = (lambda i: max(0, i - window + 1)) if win else (lambda i: i // window * window)
+            keys = sum(past + t + 1 - lo(past + t) for t in range(length)) * entries
+            moved = (2.0 * entries * G * (past + 1 - lo(past)) * Dh * 2 + n * Hq * Dh * 6) if length == 1 else None
+            ms = timed(op(ctx, "masked_attention", "sb_op_masked_attention_tiles",
+                          [q, o32, pages, table, *where, None, sink, Hq, G, Dh, Dh, Dh, win, 0, chunk, 1], [0.125]), 5, clear=True)
+            record(f"{name}_attention_{label}", ms, moved, 6.0 * keys * Hq * Dh)          # the weights go through the tensor cores as two parts
+        obf = torch.empty(n, Hq * Dh, dtype=bf, device=dev)
+        meta = ctx.entry_meta
+        ms = timed(lambda: ops.sigmoid_attention_tiles(q, obf, pages, table, meta, entries, sinks, Hq, G, Dh, Dh, window, 0.125), 5, clear=True)
+        keys_s = sum(min(window, past + t + 1) for t in range(length)) * entries
+        record("ganupel_sigmoid_attention_" + label, ms, None, 6.0 * keys_s * Hq * Dh)
+        # differential attention: 2 x 16 query heads over 2 x 4 key heads of 64, values of 128 stored once per map, every earlier key
+        Hd, Gd = 2 * H, 2 * max(H // 4, 1)
+        dpages = torch.randn(entries * per + 1, 2, Gd, page, V, device=dev).to(bf)
+        dwhere = [per, page, dpages.stride(0), dpages.stride(1), dpages.stride(2)]
+        qd = torch.randn(n, Hd * Dh, device=dev).to(bf)
+        od = torch.empty(n, Hd * V, dtype=f32, device=dev)
+        keys = sum(past + t + 1 for t in range(length)) * entries
+        moved = (entries * Gd * (past + 1) * (Dh + V) * 2.0 + n * Hd * (Dh * 2 + V * 4)) if length == 1 else None
+        ms = timed(op(ctx, "masked_attention", "sb_op_masked_attention_tiles", [qd, od, dpages, table, *dwhere, None, None, Hd, Gd, Dh, V, V, 0, 0, 0, 1],
+                      [0.125]), 5, clear=True)
+        record("differential_attention_" + label, ms, moved, 2.0 * keys * Hd * (Dh + 2 * V))
+        # what stands in front of and behind the attentions
+        wq = Hq * Dh + 2 * G * Dh
+        proj = torch.randn(n * (wq + Hq * Dh), device=dev)
+        gains = torch.ones(Hq * Dh, device=dev)
+        qo = torch.empty(n, Hq * Dh, dtype=bf, device=dev)
+        ms = timed(op(ctx, "masked_attention", "sb_op_qkv_prepare", [proj, wq + Hq * Dh, 1, 0, gains[:wq], gains, gains, 1, cs, 64, 1, 0, qo, bf, pages, table,
+                                                                    *where, Hq, G, Dh, Dh, Dh, 1], [1e-6, 0.0]), 5, clear=True)
+        record(f"qkv_prepare_norm_rotate_append_{label}", ms, n * wq * 6.0)
+        csr = torch.rand(4096, Dh // 2, 2, device=dev)
+        qkv = proj[:n * wq].view(1, n, wq)
+        ms = timed(lambda: ops.qkv_rotate_append(qkv, ctx.positions, ctx.slots, csr, Dh, qo, pages, table, Hq, G, Dh, Dh), 5, clear=True)
+        record(f"ganupel_qkv_rotate_append_{label}", ms, n * wq * 6.0)
+        y = torch.empty(n, Hq * Dh, dtype=bf, device=dev)
+        ms = timed(op(ctx, "masked_attention", "sb_op_head_gate", [o32, proj, wq + Hq * Dh, 1, 0, wq, y, bf, Hq, G, Dh, 1, 0], [0.0, 1.0, 1e-6]), 5, clear=True)
+        record(f"head_gate_elementwise_{label}", ms, n * Hq * Dh * 10.0)
+        yd = torch.empty(n, H * V, dtype=bf, device=dev)
+        ms = timed(op(ctx, "masked_attention", "sb_op_head_gate", [od, proj, wq + Hq * Dh, 1, 0, wq, yd, bf, H, Gd // 2, V, 2, 1], [0.7, 0.5, 1e-6]), 5, clear=True)
+        record(f"head_gate_differential_{label}", ms, n * H * V * 10.0)
+        # retention: rotation, the decayed recurrence (Keralorn's kernel, fed ready-made), norm and gate per head
+        wr = 2 * H * D + 2 * H * V
+        rproj = torch.randn(n * wr, device=dev)
+        ready = torch.empty(n * (2 * H * D + H * V), device=dev)
+        ms = timed(op(ctx, "lightning", "sb_op_rotate_qk", [rproj, wr, 1, 0, 0, H * D, 2 * H * D, cs, 64, 0, ready, H, D, V], [D ** -0.5]), 5, clear=True)
+        record(f"retention_rotate_{label}", ms, n * (2 * H * D + H * V) * 8.0)
+        state = torch.zeros(entries + 1, H, D, V, device=dev)
+        decay = torch.full((H,), 0.98, device=dev)
+        ro = torch.empty(n, H * V, device=dev)
+        ms = timed(op(ctx, "lightning", "sb_op_lightning_scan", [ready, 2 * H * D + H * V, 1, 0, 0, H * D, 2 * H * D, decay, state, ro, H, D, V, None, 1]), 5,
+                   clear=True)
+        record(f"retention_recurrence_{label}", ms, (2.0 * entries * H * D * V * 4) if length == 1 else None, 4.0 * n * H * D * V,
+               note="float32 arithmetic: the fraction is of the tensor-core peak only for scale")
+        ry = torch.empty(n, H * V, dtype=bf, device=dev)
+        ms = timed(op(ctx, "lightning", "sb_op_group_norm_gate", [ro, rproj, wr, 1, 0, 2 * H * D + H * V, None, 0, ry, bf, H, V, 1], [1e-6]), 5, clear=True)
+        record(f"group_norm_gate_{label}", ms, n * H * V * 10.0)
+        # the gated delta rule: convolution, unit vectors, decays; the recurrence
+        C, ra = 2 * H * D + H * V, 64
+        w1, w2 = C + H + 2 * ra, H * D + H * V
+        p1, p2 = torch.randn(n * w1, device=dev) * 0.5, torch.randn(n * w2, device=dev) * 0.5
+        conv = torch.randn(C, 4, device=dev) * 0.3
+        record_elems = H * D * V + 3 * C
+        rec = torch.zeros(entries + 1, record_elems, device=dev)
+        dready = torch.empty(n * (C + H + H * D), device=dev)
+        alog, dtb = torch.zeros(H, device=dev), torch.full((H * D,), -4.0, device=dev)
+        ms = timed(op(ctx, "delta_rule", "sb_op_delta_prepare", [p1, w1, 1, p2, w2, 1, 0, conv, alog, dtb, rec, record_elems, H * D * V, dready, H, H, D, V, 4]),
+                   5, clear=True)
+        record(f"delta_prepare_{label}", ms, n * (C * 8.0 + H * D * 8.0))
+        do = torch.empty(n, H * V, device=dev)
+        ms = timed(op(ctx, "delta_rule", "sb_op_delta_scan", [dready, rec, record_elems, do, H, H, D, V]), 5, clear=True)
+        record(f"delta_recurrence_{label}", ms, (2.0 * entries * H * D * V * 4) if length == 1 else None, 8.0 * n * H * D * V,
+               note="float32 arithmetic: the fraction is of the tensor-core peak only for scale")
+        gproj = torch.rand(n, 3 * H * D + H * V, device=dev)
+        go = torch.empty(n, H * V, device=dev)
+        gstate = torch.zeros(entries + 1, H, D, V, device=dev)
+        try:
+            ms = timed(lambda: ops.gated_scan(gproj, 0, H * D, 2 * H * D, 3 * H * D, meta, entries, gstate, go, H, D, V), 5, clear=True)
+            record(f"ganupel_gated_recurrence_{label}", ms, (2.0 * entries * H * D * V * 4) if length == 1 else None, 6.0 * n * H * D * V)
+        except (AttributeError, TypeError, RuntimeError) as e:
+            kern[f"ganupel_gated_recurrence_{label}"] = {"unavailable": str(e)[:120]}
+        # the folds: two branches normed one by one; the per-layer token input's cast and gate
+        h = torch.randn(n, width, device=dev)
+        a_, b_ = torch.randn(n, width, device=dev), torch.randn(n, width, device=dev)
+        parts = torch.randn(2 * n * width, device=dev)
+        gain = torch.ones(width, device=dev)
+        ms = timed(op(ctx, "branch", "sb_op_branch_pair_norm_fold", [h, a_, parts, 1, 0, b_, parts[n * width:], 1, 0, gain, gain, f32, width], [0.5, 0.5, 1e-6]),
+                   5, clear=True)
+        record(f"branch_pair_norm_fold_{label}", ms, n * width * 32.0)
+        gb = torch.ones(width, dtype=bf, device=dev)
+        ms = timed(lambda: ops.branch_norm_fold(h, gb, 1e-6, a=a_, a_partials=parts[:2 * n * width].view(2, n, width)), 5, clear=True)
+        record(f"pusisun_branch_norm_fold_{label}", ms, n * width * 24.0)
+        x = torch.empty(n, width, dtype=bf, device=dev)
+        ms = timed(op(ctx, "elementwise", "sb_op_stream_cast", [h, parts, 1, 0, x, bf, width]), 5, clear=True)
+        record(f"stream_cast_{label}", ms, n * width * 14.0)
+        table_s = torch.randn(32000, 4 * 256, device=dev).to(bf)
+        gsum, gout = torch.randn(n * 256, device=dev), torch.empty(n, 256, dtype=bf, device=dev)
+        ms = timed(op(ctx, "elementwise", "sb_op_token_gate", [gsum, 256, 1, 0, table_s, bf, 1024, 256, 32000, None, gout, bf, 1]), 5, clear=True)
+        record(f"token_gate_{label}", ms, n * 256 * 8.0)
+    return kern
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -752,7 +916,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="1b: the decode step (default); 3b, 8b: serving runs")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64, float32 and prefill measurements")
-    ap.add_argument("--design", default="", choices=["", "keralorn", "ganupel", "pusisun"],
+    ap.add_argument("--design", default="", choices=["", "keralorn", "ganupel", "pusisun", "sitivik"],
                     help="keralorn: prefill and decode of that design beside a Llama of equal layer sizes, and its own kernels alone; "
                          "ganupel: the same beside Keralorn and Llama; pusisun: the same beside Ganupel and Llama")
     a = ap.parse_args()

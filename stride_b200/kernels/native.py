@@ -332,7 +332,9 @@ class ImmediateProgram:
         if self.pending is not None:
             raise NotNative(f"{who} adds to the residual stream while partial sums are pending on it")
 
-    def add(self, library_name: str, function: str, ints, floats=(), chain=None) -> None:
+    def prepared(self, library_name: str, function: str, ints, floats=()):
+        """The operation as a callable that launches it for this program's step, every time it is called (its arguments are read once,
+        here): what a measurement that launches one operation many times needs."""
         if len(ints) > OP_INTS or len(floats) > OP_FLOATS:
             raise ValueError(f"{function}: too many arguments for one operation")
         lib = library(library_name)
@@ -341,12 +343,20 @@ class ImmediateProgram:
             fn.restype, fn.argtypes = c_int, [ctypes.POINTER(SbOp), ctypes.POINTER(SbStep), c_void_p]
             fn._sb_typed = True
         op = SbOp()
+        keep = [v for v in ints if isinstance(v, torch.Tensor)]
         for k, v in enumerate(ints):
             op.i[k] = _value(v)
         for k, v in enumerate(floats):
             op.f[k] = float(v)
-        rc = fn(ctypes.byref(op), ctypes.byref(self.step), ops._stream())
-        if rc == 1:
-            raise RuntimeError(f"{function}: " + lib.sb_last_error().decode(errors="replace"))
-        if rc == 0:
-            ops.launches += 1
+        op_p, step_p = ctypes.byref(op), ctypes.byref(self.step)
+
+        def launch(_keep=(op, keep, self)):
+            rc = fn(op_p, step_p, ops._stream())
+            if rc == 1:
+                raise RuntimeError(f"{function}: " + lib.sb_last_error().decode(errors="replace"))
+            if rc == 0:
+                ops.launches += 1
+        return launch
+
+    def add(self, library_name: str, function: str, ints, floats=(), chain=None) -> None:
+        self.prepared(library_name, function, ints, floats)()

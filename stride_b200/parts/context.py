@@ -123,3 +123,26 @@ class StepContext:
     @property
     def decode_only(self) -> bool:
         return all(l == 1 for l in self.entry_length)
+
+
+def step_context(entries, workspace: Workspace, compute_dtype: torch.dtype, tokens=None, rows: int = 0) -> StepContext:
+    """A `StepContext` for a step given as (slot, length, first position) per entry, its integer inputs in one device buffer in the step
+    program's layout (tokens, positions, slots, wanted rows and entry records, each `rows` apart): what measurements and tools that drive
+    single parts or operations by hand need."""
+    n = sum(e[1] for e in entries)
+    R = max(rows, workspace.max_tokens, n, len(entries))
+    ints = torch.zeros(9 * R + 64, dtype=torch.int32)
+    at = 0
+    for k, (slot, length, first) in enumerate(entries):
+        ints[R + at:R + at + length] = torch.arange(first, first + length, dtype=torch.int32)
+        ints[2 * R + at:2 * R + at + length] = slot
+        for j, v in enumerate((slot, at, length, first)):
+            ints[4 * R + j * R + k] = v
+        at += length
+    if tokens is not None:
+        ints[:n] = torch.as_tensor(tokens, dtype=torch.int32)
+    d = ints.to(workspace.device)
+    E = len(entries)
+    return StepContext(n=n, token_ids=d[0:n], positions=d[R:R + n], slots=d[2 * R:2 * R + n], workspace=workspace, compute_dtype=compute_dtype,
+                       entry_slots=[e[0] for e in entries], entry_first_row=[int(ints[5 * R + k]) for k in range(E)],
+                       entry_length=[e[1] for e in entries], entry_first_pos=[e[2] for e in entries], entry_meta=d[4 * R:8 * R].view(4, R)[:, :E])
