@@ -890,7 +890,7 @@ def _sitivik_kernels(timed, pk: dict, width: int, ff: int) -> dict:
         a_, b_ = torch.randn(n, width, device=dev), torch.randn(n, width, device=dev)
         parts = torch.randn(2 * n * width, device=dev)
         gain = torch.ones(width, device=dev)
-        ms = timed(op(ctx, "branch", "sb_op_branch_pair_norm_fold", [h, a_, parts, 1, 0, b_, parts[n * width:], 1, 0, gain, gain, f32, width], [0.5, 0.5, 1e-6]),
+        ms = timed(op(ctx, "branch", "sb_op_branch_pair_norm_fold", [h, a_, parts, 1, 0, b_, parts[n * width:], 1, gain, gain, f32, width], [0.5, 0.5, 1e-6]),
                    5, clear=True)
         record(f"branch_pair_norm_fold_{label}", ms, n * width * 32.0)
         gb = torch.ones(width, dtype=bf, device=dev)

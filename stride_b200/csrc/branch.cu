@@ -315,7 +315,7 @@ SB_EXPORT int sb_op_row_scaled_add(const SbOp* op, const SbStep* s, void* stream
 // normed one by one. A block per row, both rows held in shared memory between the sums of squares and the add.
 namespace {
 
-template <class TG>
+template <class TG, bool VEC>
 __global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ ga,
                                                                     const TG* __restrict__ gb, int W, float eps) {
   extern __shared__ __align__(16) float row_values[];      // [2][W]
@@ -324,6 +324,24 @@ __global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __res
   sb::grid_dependency_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
   float sa = 0.0f, sb2 = 0.0f;
+  if (VEC) {      // four elements a thread and request; the squares of a thread's elements in ascending columns, as in the scalar form per element
+    float4* held = reinterpret_cast<float4*>(row_values);
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      const int64_t i = (row + c) / 4;
+      const float4 va = source_value<float4>(a, i), vb = source_value<float4>(b, i);
+      held[c / 4] = va, held[(W + c) / 4] = vb;
+      sa = fmaf(va.x, va.x, sa), sa = fmaf(va.y, va.y, sa), sa = fmaf(va.z, va.z, sa), sa = fmaf(va.w, va.w, sa);
+      sb2 = fmaf(vb.x, vb.x, sb2), sb2 = fmaf(vb.y, vb.y, sb2), sb2 = fmaf(vb.z, vb.z, sb2), sb2 = fmaf(vb.w, vb.w, sb2);
+    }
+    const float ra = mul(a.c, 1.0f / sqrtf(sb::block_sum(sa, red) / static_cast<float>(W) + eps));
+    const float rb = mul(b.c, 1.0f / sqrtf(sb::block_sum(sb2, red) / static_cast<float>(W) + eps));
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      const float4 va = mul(mul(held[c / 4], ra), gain4<TG>(ga, c)), vb = mul(mul(held[(W + c) / 4], rb), gain4<TG>(gb, c));
+      float4* d = reinterpret_cast<float4*>(dst) + (row + c) / 4;
+      *d = add(*d, add(va, vb));
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     const float va = source_value<float>(a, row + c), vb = source_value<float>(b, row + c);
     row_values[c] = va, row_values[W + c] = vb;
@@ -358,16 +376,24 @@ SB_EXPORT int sb_op_branch_pair_norm_fold(const SbOp* op, const SbStep* s, void*
   if (smem > 160 * 1024) return sb::fail("sb_op_branch_pair_norm_fold: rows of %d elements do not fit the row buffer", W), SB_OP_FAILED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int threads = W >= 1024 ? 256 : 128;
+  // which form runs depends on the width and the buffers alone, never on the rows of the step
+  const bool vec = W % 4 == 0 && stride % 4 == 0 && aligned16(ptr<float>(op->i[0])) && aligned16(a) && aligned16(pa) && aligned16(b) && aligned16(pb) &&
+                   aligned16(ptr<const void>(op->i[8])) && aligned16(ptr<const void>(op->i[9]));
+#define SB_PAIR(TG, VEC)                                                                                                                        \
+  do {                                                                                                                                          \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<TG, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    sb::launch_pdl(branch_pair_norm_fold_kernel<TG, VEC>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const TG>(op->i[8]), \
+                   ptr<const TG>(op->i[9]), W, static_cast<float>(op->f[2]));                                                                   \
+  } while (0)
   if (op->i[10] == 0) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(branch_pair_norm_fold_kernel<float>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const float>(op->i[8]),
-                   ptr<const float>(op->i[9]), W, static_cast<float>(op->f[2]));
+    if (vec) SB_PAIR(float, true);
+    else SB_PAIR(float, false);
   } else if (op->i[10] == 1) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(branch_pair_norm_fold_kernel<bf16>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const bf16>(op->i[8]),
-                   ptr<const bf16>(op->i[9]), W, static_cast<float>(op->f[2]));
+    if (vec) SB_PAIR(bf16, true);
+    else SB_PAIR(bf16, false);
   } else {
     return sb::fail("sb_op_branch_pair_norm_fold: unsupported gain dtype %d", (int)op->i[10]), SB_OP_FAILED;
   }
+#undef SB_PAIR
   return sb::check_launch("sb_op_branch_pair_norm_fold");
 }

@@ -459,7 +459,9 @@ __global__ void __launch_bounds__(128) masked_attention_tile_kernel(TileParams p
   bf16* Qs = reinterpret_cast<bf16*>(tmax + 4 * 16);            // [16][ldk]
   bf16* stage0 = Qs + 16 * ldk;
   const int stage_elems = KT * (ldk + (own_values ? ldv : 0));
-  int e = 0, tile = blockIdx.x, len = 0;
+  // the blocks that start first take the last tiles: the last positions of an entry see the most keys (a full window, the end of a chunk),
+  // and a launch that ends with its longest blocks leaves SMs idle behind them
+  int e = 0, tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), len = 0;
   for (; e < p.entries; ++e) {
     len = p.meta[2 * p.meta_stride + e];
     const int tiles = (len + PT - 1) / PT;
