@@ -574,3 +574,97 @@ def test_command_line_generates_what_the_entry_point_generates(sitivik_dirs, tmp
                   max_context=128, device=DEV)
         want = llm.generate(prompts, max_new_tokens=6)
         assert [g["tokens"] for g in got] == [w.tokens for w in want] and all(g["finish"] == "length" for g in got)
+
+
+def _drawn_configuration(seed):
+    """A configuration drawn at random: sizes that are no multiple of four or eight, one tap, heads that are their own key heads, masks of
+    one token and masks longer than the request, layers in any order, with and without the token input, feed-forward and rotation."""
+    import random
+    r = random.Random(seed)
+    even = lambda lo, hi: 2 * r.randint(lo // 2, hi // 2)
+
+    def rot(dim, scaled):
+        if r.random() < 0.25:
+            return None
+        dims = even(2, dim)
+        scaling = (r.choice([2.0, 8.0]), 1.0, r.choice([2.0, 4.0]), r.choice([16, 64, 512])) if scaled and r.random() < 0.6 else None
+        out = {"dims": dims, "base": r.choice([50.0, 10000.0, 1000000.0])}
+        if scaling:
+            out["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+        return out
+
+    def left(masked):
+        kv = r.randint(1, 3)
+        dim = even(4, 40)
+        m = {"heads": kv * r.randint(1, 4), "kv_heads": kv, "dim": dim, "vdim": r.randint(3, 40), "scale": dim ** -0.5}
+        if masked:
+            m["mask"] = {"size": r.choice([1, 2, 5, 16, 33, 64, 500])}
+        ro = rot(dim, True)
+        if ro and masked:
+            m["rot"] = ro
+        return m
+
+    layers = []
+    for _ in range(r.randint(2, 4)):
+        kind = r.choice(["parallel", "attention", "parallel_2"])
+        mlp = {"kind": "dense", "ff": r.randint(5, 60)} if r.random() < 0.7 else None
+        if kind == "attention":
+            m = left(False)
+            m["diff"] = r.choice([0.2, 0.5, 0.8])
+            if r.random() < 0.6:
+                m["q_temp"] = {"coef": r.choice([0.1, 0.5]), "every": r.choice([1, 3, 16, 1000])}
+        elif kind == "parallel":
+            heads, dim = r.randint(1, 4), even(4, 36)
+            right = {"heads": heads, "dim": dim, "vdim": r.randint(2, 40), "decay": [r.choice([0.5, 0.9, 0.99, 1.0]) for _ in range(heads)]}
+            ro = rot(dim, False)
+            if ro:
+                right["rot"] = ro
+            m = {"left": left(True), "right": right}
+        else:
+            kv = r.randint(1, 3)
+            right = {"heads": kv * r.randint(1, 3), "kv_heads": kv, "dim": r.randint(3, 40), "vdim": r.randint(2, 36), "conv": r.randint(1, 5),
+                     "decay_rank": r.randint(1, 12), "gate_rank": r.randint(1, 12)}
+            m = {"left": left(True), "right": right, "left_scale": r.choice([0.5, 1.0, 1.5]), "right_scale": r.choice([0.5, 1.0, 2.0])}
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Sitivik", "vocab": r.randint(30, 300), "width": r.choice([40, 50, 64, 72, 100, 136]), "norm": {"eps": r.choice([1e-6, 1e-4])},
+           "layers": layers}
+    if r.random() < 0.7:
+        cfg["embedding"] = {"scale": r.choice([0.5, 1.0, 4.0])}
+    if r.random() < 0.7:
+        cfg["token_side"] = {"dim": r.randint(1, 20)}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Whole, and in portions down to one token with pages trimmed on the way, in 32-bit against the plain implementation and in bfloat16 in
+    equal bits between the two ways of feeding."""
+    from stride_b200.engine.engine import StepEntry
+    import sitivik_cases
+    cfg = _drawn_configuration(seed)
+    sitivik_cases.SITIVIK[f"R{seed}"] = (cfg, seed, 16)
+    try:
+        folder = write_model(tmp_path / "m", f"R{seed}")
+    finally:
+        del sitivik_cases.SITIVIK[f"R{seed}"]
+    pcfg, w = load_plain(folder)
+    toks = random_tokens(cfg["vocab"], 75, seed)
+    want = plain.forward(pcfg, w, toks).float()
+    for dtype in ("float32", "bfloat16"):
+        got = []
+        for cuts in ([75], [9, 1, 2, 30, 1, 1, 17, 5, 1, 1, 7]):
+            eng = _engine(folder, dtype, 16, 12)
+            slot = eng.cache.acquire_slot()
+            rows, at = [], 0
+            for n in cuts:
+                eng.cache.ensure(slot, at + n)
+                rows.append(eng.step([StepEntry(slot, at, toks[at:at + n], list(range(n)))]).cpu().clone())
+                eng.cache.trim(slot)
+                at += n
+            got.append(torch.cat(rows))
+        assert torch.equal(got[0], got[1]), f"seed {seed} {dtype}: in portions it differs from the whole"
+        if dtype == "float32":
+            assert (got[0] - want).abs().max() <= logit_tolerance("float32", want), f"seed {seed}: {cfg}"
+        else:
+            noise = _noise(pcfg, w, toks)[0]
+            assert (got[0] - plain.forward(pcfg, w, toks, True).float()).abs().max() <= 2.0 * noise
