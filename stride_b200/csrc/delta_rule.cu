@@ -5,7 +5,7 @@
 //   S <- diag(g_t) S          g_t [D] in (0, 1): one decay per key channel
 //   u  = beta_t (v_t - S^T k_t)
 //   S <- S + k_t u^T
-//   o_t = S^T q_t             (the read-out sees the token's own write)
+//   o_t = S^T q_t             (read after the write: a token's own pair already counts)
 //
 // A column of S depends on no other column, so a thread owns a slice of one column and the columns are spread over threads and CTAs; the
 // two sums over the key channels are made per thread in ascending channels and then over the P threads of a column by xor shuffles, P a

@@ -242,7 +242,7 @@ struct AttnParams {
   int H, G, D, Dv, Dc;
   int window, keep_first;
   float scale;
-  int chunk;                 // > 0: a row sees only the keys of its own chunk of this many positions, counted from position 0
+  int chunk;                 // > 0: a row sees only the keys of its own chunk of this many positions (borders at multiples of it)
   int out_f32;               // 1: `out` is float32 whatever the storage of q and the cache
 };
 

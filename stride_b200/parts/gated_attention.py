@@ -3,11 +3,11 @@
 q, k, v = W x (+ b); q and k may be RMS-normed, over the whole projection (gains of that size) or per head (one gain of the head's size
 for all heads); the first `rotary_dim` elements of every q and k head may be rotated by the position (a position part's table; pairs
 (2i, 2i + 1) when `interleaved`, else (i, i + rotary_dim / 2)); q may grow with the position, times 1 + c ln(floor((p + 1) / every) + 1).
-score = scale q.k; i sees j <= i with i - j < window (if a window is set) and floor(i / chunk) = floor(j / chunk) (if chunks are set,
-counted from position 0 of the sequence); ordinary softmax, or with one more term exp(0) in the denominator (`sink` "zero": a key of score 0
+score = scale q.k; i sees j <= i with i - j < window (if a window is set) and floor(i / chunk) = floor(j / chunk) (if chunks are set:
+their borders are absolute positions, wherever a prompt was cut); ordinary softmax, or with one more term exp(0) in the denominator (`sink` "zero": a key of score 0
 without a value). The heads' results are multiplied by sigmoid(W_g x), one gate per element or one per head, and projected by W_o (+ b).
 
-With `maps` 2 (differential attention) a head has two queries and a key head two keys, stored head by head as [map 1 | map 2]; the two
+With `maps` 2 (differential attention) a head has two queries and a key head two keys, the second behind the first in the head's rows; the two
 softmax maps share the values, and the head's result is a1 - lambda a2 with lambda = exp(lq1.lk1) - exp(lq2.lk2) + diff, RMS-normed over
 the head's values (no gain), times 1 - diff. The kernels see 2 H query heads over 2 G key heads: the query rows are reordered so that
 the heads of a (key head, map) lie side by side, and the value rows are stored once per map."""
