@@ -15,7 +15,8 @@ the embedding is scaled; the head is the embedding table. The mixers:
 config.json keys read here:
   architecture "Sitivik"; vocab, width; norm.eps; embedding.scale (absent: 1); token_side.dim (absent: no per-layer token input);
   layers[i]: type, mixer {...}, mlp ({kind "dense", ff} | null);
-    attention members: heads, kv_heads, dim, vdim, scale, mask.size, rot {dims, base, scaling {factor, low, high, original}} (absent: no rotation);
+    attention members: heads, kv_heads, dim, vdim, scale, mask.size (absent: every earlier key), rot {dims, base, scaling {factor, low, high,
+    original}} (absent: no rotation);
     "attention" also: diff, q_temp {coef, every} (absent: none); retention: heads, dim, vdim, decay [heads], rot {dims, base};
     gated delta rule: heads, kv_heads, dim, vdim, conv; "parallel_2" also: left_scale, right_scale.
   The ranks of the delta rule's two low-rank projections are sizes that only the tensors' shapes tell: `with_tensor_shapes` writes them
@@ -132,7 +133,7 @@ class SitivikConfig:
             heads, kv, dim, vdim = (_get(m, k, w, int, True) for k in ("heads", "kv_heads", "dim", "vdim"))
             if heads % kv:
                 raise ConfigError(f"config.json: '{w}heads' {heads} is no multiple of kv_heads {kv}")
-            mask = _get(_get(m, "mask", w), "size", w + "mask.", int, True) if masked else 0
+            mask = _get(m["mask"], "size", w + "mask.", int, True) if masked and m.get("mask") else 0      # (no mask: every earlier key)
             qt = m.get("q_temp")
             q_temp = (_get(qt, "coef", w + "q_temp.", float), _get(qt, "every", w + "q_temp.", int, True)) if qt else None
             return SoftmaxMember(heads, kv, dim, vdim, _get(m, "scale", w, float), mask, rotation(m, w),

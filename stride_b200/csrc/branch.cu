@@ -309,15 +309,15 @@ SB_EXPORT int sb_op_row_scaled_add(const SbOp* op, const SbStep* s, void* stream
 // ---------------------------------------------------------------------------------------------------------------------------------
 // Two branches that are each RMS-normed over their row, with a gain of their own, before their weighted sum joins `dst`:
 //
-//   dst[r, j] += ca * ga[j] * A[r, j] / sqrt(mean_j(A[r, :]^2) + eps) + cb * gb[j] * B[r, j] / sqrt(mean_j(B[r, :]^2) + eps)
+//   dst[r, j] += w[j] * (ca * ga[j] * A[r, j] / sqrt(mean_j(A[r, :]^2) + eps) + cb * gb[j] * B[r, j] / sqrt(mean_j(B[r, :]^2) + eps))
 //
-// with A = a + (pa_0 + pa_1 + ..), B likewise; the branch buffers are zero afterwards. What mixers side by side need whose results are
+// with A = a + (pa_0 + pa_1 + ..), B likewise, and w a gain on the sum (a layer scale) or none; the branch buffers are zero afterwards. What mixers side by side need whose results are
 // normed one by one. A block per row, both rows held in shared memory between the sums of squares and the add.
 namespace {
 
 template <class TG, bool VEC>
 __global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ ga,
-                                                                    const TG* __restrict__ gb, int W, float eps) {
+                                                                    const TG* __restrict__ gb, const TG* __restrict__ outer, int W, float eps) {
   extern __shared__ __align__(16) float row_values[];      // [2][W]
   __shared__ float red[32];
   sb::grid_launch_dependents();
@@ -338,7 +338,9 @@ __global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __res
     for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
       const float4 va = mul(mul(held[c / 4], ra), gain4<TG>(ga, c)), vb = mul(mul(held[(W + c) / 4], rb), gain4<TG>(gb, c));
       float4* d = reinterpret_cast<float4*>(dst) + (row + c) / 4;
-      *d = add(*d, add(va, vb));
+      float4 v = add(va, vb);
+      if (outer != nullptr) v = mul(v, gain4<TG>(outer, c));
+      *d = add(*d, v);
     }
     return;
   }
@@ -351,14 +353,16 @@ __global__ void __launch_bounds__(256) branch_pair_norm_fold_kernel(float* __res
   const float rb = mul(b.c, 1.0f / sqrtf(sb::block_sum(sb2, red) / static_cast<float>(W) + eps));
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     const float va = mul(mul(row_values[c], ra), sb::widen(ga[c])), vb = mul(mul(row_values[W + c], rb), sb::widen(gb[c]));
-    dst[row + c] = add(dst[row + c], add(va, vb));
+    float v = add(va, vb);
+    if (outer != nullptr) v = mul(v, sb::widen(outer[c]));
+    dst[row + c] = add(dst[row + c], v);
   }
 }
 
 }  // namespace
 
 // i: 0 dst, 1 a, 2 a's partial sums (flat), 3 their K ranges S, 4 most tokens with a buffer per range, 5 b, 6 b's partial sums, 7 their S,
-//    8 a's gain, 9 b's gain, 10 the gains' dtype, 11 W
+//    8 a's gain, 9 b's gain, 10 the gains' dtype, 11 W, 12 a gain on the sum, of the same dtype (or 0)
 // f: 0 ca, 1 cb, 2 eps
 SB_EXPORT int sb_op_branch_pair_norm_fold(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
@@ -378,12 +382,12 @@ SB_EXPORT int sb_op_branch_pair_norm_fold(const SbOp* op, const SbStep* s, void*
   const int threads = W >= 1024 ? 256 : 128;
   // which form runs depends on the width and the buffers alone, never on the rows of the step
   const bool vec = W % 4 == 0 && stride % 4 == 0 && aligned16(ptr<float>(op->i[0])) && aligned16(a) && aligned16(pa) && aligned16(b) && aligned16(pb) &&
-                   aligned16(ptr<const void>(op->i[8])) && aligned16(ptr<const void>(op->i[9]));
+                   aligned16(ptr<const void>(op->i[8])) && aligned16(ptr<const void>(op->i[9])) && aligned16(ptr<const void>(op->i[12]));
 #define SB_PAIR(TG, VEC)                                                                                                                        \
   do {                                                                                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(branch_pair_norm_fold_kernel<TG, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     sb::launch_pdl(branch_pair_norm_fold_kernel<TG, VEC>, dim3(s->n), dim3(threads), smem, st, ptr<float>(op->i[0]), A, B, ptr<const TG>(op->i[8]), \
-                   ptr<const TG>(op->i[9]), W, static_cast<float>(op->f[2]));                                                                   \
+                   ptr<const TG>(op->i[9]), ptr<const TG>(op->i[12]), W, static_cast<float>(op->f[2]));                                         \
   } while (0)
   if (op->i[10] == 0) {
     if (vec) SB_PAIR(float, true);

@@ -54,6 +54,7 @@ def emit_on_branch(program, branch: torch.Tensor, emit) -> tuple:
 class LayerScale(BranchScale):
     """params: size. tensors: weight [size]."""
     graph_safe = True
+    gain_only = True          # nothing but a gain vector: a part that folds its own result (`emit_scaled`) may apply it on the way
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -151,6 +152,9 @@ class _ScaledBlock(Block):
         width = stream.h.shape[1]
         x = ctx.workspace.get("block.x", ctx.n, (width,), ctx.act_dtype)
         norm.forward(ctx, stream, x)
+        if hasattr(part, "forward_scaled") and getattr(scale, "gain_only", False):
+            stream.fold()
+            return run(lambda c, x_, *rest: part.forward_scaled(c, x_, stream, *rest, scale.weight), x)
         if hasattr(part, "forward_sources"):
             sources = run(part.forward_sources, x)
         else:
@@ -163,6 +167,9 @@ class _ScaledBlock(Block):
         ws, width = program.workspace, program.h.shape[1]
         x = ws.get("block.x", ws.max_tokens, (width,), self.env.act_dtype)
         norm.emit(program, x)
+        if hasattr(part, "emit_scaled") and getattr(scale, "gain_only", False):
+            program.need_folded("a sublayer that folds its own result")
+            return run(lambda pr, x_, *rest: part.emit_scaled(pr, x_, *rest, scale.weight), x)
         if hasattr(part, "emit_sources"):
             sources = run(part.emit_sources, x)
         else:

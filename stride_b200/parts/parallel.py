@@ -85,7 +85,7 @@ class NormedParallelMixer(Mixer):
             raise ValueError("parallel mixer with norms: two members, two constants and two gains")
         self.members = [part_class("mixer", m.kind)(m, env) for m in members]
         self.graph_safe = all(m.graph_safe for m in self.members)
-        self.gains = None
+        self.gains = self._outer = None
 
     def tensor_plan(self):
         from .spec import TensorPlan
@@ -113,7 +113,19 @@ class NormedParallelMixer(Mixer):
         with ImmediateProgram(ctx, stream) as program:
             self.emit(program, x, cache)
 
-    def emit(self, program, x, cache):
+    def forward_scaled(self, ctx, x, stream, cache, gain):
+        from ..kernels.native import ImmediateProgram
+        with ImmediateProgram(ctx, stream) as program:
+            self.emit_scaled(program, x, cache, gain)
+
+    def emit_scaled(self, program, x, cache, gain):
+        """The result times a gain vector of the width (a layer scale), added to the program's stream by the same pass that norms the members."""
+        key = id(gain)
+        if self._outer is None or self._outer[0] != key:
+            self._outer = (key, gain.to(torch.float32).contiguous())
+        self.emit(program, x, cache, self._outer[1])
+
+    def emit(self, program, x, cache, outer=None):
         ws = program.workspace
         buffers = [ws.get(f"parallel.branch{k}", ws.max_tokens, (self.hidden,), torch.float32) for k in range(2)]
         (a, pa), (b, pb) = [emit_on_branch(program, buf, lambda m=m, c=c: m.emit(program, x, c))
@@ -121,5 +133,5 @@ class NormedParallelMixer(Mixer):
         (fa, Sa, _), (fb, Sb, _) = pa or (None, 1, 0), pb or (None, 1, 0)
         program.need_folded("mixers side by side")
         program.add("branch", "sb_op_branch_pair_norm_fold",
-                    [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, self.gains[0], self.gains[1], self.gains[0].dtype, self.hidden],
+                    [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, self.gains[0], self.gains[1], self.gains[0].dtype, self.hidden, outer],
                     [self.scales[0], self.scales[1], self.eps])
