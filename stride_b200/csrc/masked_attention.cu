@@ -1079,7 +1079,7 @@ __global__ void __launch_bounds__(128) head_gate_kernel(HeadGateParams p) {
   sb::grid_dependency_wait();
   const float* gate = p.proj + static_cast<int64_t>(row) * p.width + p.g_off;
   T* out = static_cast<T*>(p.out) + static_cast<int64_t>(row) * p.H * p.Dv;
-  for (int h = warp; h < p.H; h += warps) {
+  for (int h = blockIdx.y * warps + warp; h < p.H; h += gridDim.y * warps) {      // a warp per head; how the heads are dealt to blocks changes nothing
     const int g = h / Hg, j = h % Hg;
     const float* a1 = p.a + (static_cast<int64_t>(row) * p.maps * p.H + (p.maps == 2 ? (2 * g) * Hg + j : h)) * p.Dv;
     const float* a2 = a1 + static_cast<int64_t>(Hg) * p.Dv;
@@ -1151,8 +1151,10 @@ SB_EXPORT int sb_op_head_gate(const SbOp* op, const SbStep* s, void* stream) {
                    width, (int)op->i[5], ptr<void>(op->i[6]), H, G, (int)op->i[10], maps, (int)op->i[12], (float)op->f[0], (float)op->f[1],
                    (float)op->f[2]};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (op->i[7] == 0) sb::launch_pdl(head_gate_kernel<float>, dim3(s->n), dim3(128), 0, st, p);
-  else if (op->i[7] == 1) sb::launch_pdl(head_gate_kernel<bf16>, dim3(s->n), dim3(128), 0, st, p);
+  int shares = (4 * sb::sm_count() + s->n - 1) / s->n;          // blocks enough to fill the device when the tokens are few
+  shares = shares < 1 ? 1 : shares > (H + 3) / 4 ? (H + 3) / 4 : shares;
+  if (op->i[7] == 0) sb::launch_pdl(head_gate_kernel<float>, dim3(s->n, shares), dim3(128), 0, st, p);
+  else if (op->i[7] == 1) sb::launch_pdl(head_gate_kernel<bf16>, dim3(s->n, shares), dim3(128), 0, st, p);
   else return sb::fail("sb_op_head_gate: unsupported dtype %d", (int)op->i[7]), SB_OP_FAILED;
   return sb::check_launch("sb_op_head_gate");
 }
